@@ -1,0 +1,504 @@
+"""Benchmark of the scaled-quantization cast path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--exchange peer|nccl] [--no-extras]
+
+Headline workload: the row-sharded per-tensor dynamic FP8 cast of a bf16
+131072 x 8192 tensor (2 GiB), split by rows over N GPUs (strong scaling: the total
+is fixed).  One step = local amax kernel -> amax exchange -> saturated e4m3 cast.
+`value` is algorithmic GB/s (5 bytes per element: the shard does not fit in L2, so
+the input is read twice and the output written once) summed over all ranks, timed
+with CUDA events, max over ranks.  `e2e` is the same metric through the public
+Python entry point with pinned HOST input and output buffers, the copies inside the
+timed region.  One JSON line on stdout from rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "quant_cast_hbm_bandwidth"
+UNIT = "GB/s"
+HEADLINE = "fp8_sharded"
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi samples of one GPU while the timed kernels run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.rows:
+            if t < t0 or t > t1 + 0.1:
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+def cpu_reference_pass(name, x):
+    """One pass of the reference's CPU (eager PyTorch) arithmetic for workload `name`,
+    through the oracle port.  Returns nothing; the caller times it."""
+    import torch
+
+    import oracle
+
+    if name in ("fp8_sharded", "fp8_tensor"):
+        oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)
+    elif name == "fp8_rowwise":
+        oracle.fp8_rowwise_quant(x, torch.float8_e4m3fn)
+        oracle.fp8_rowwise_quant(x, torch.float8_e5m2)
+    elif name == "mxfp8":
+        _, s = oracle.mxfp8_quantize(x, "ceil")
+        oracle.to_blocked(s)
+        _, s = oracle.mxfp8_quantize(x.t().contiguous(), "ceil")
+        oracle.to_blocked(s)
+    elif name == "nvfp4":
+        _, s, _ = oracle.nvfp4_quantize(x)
+        oracle.to_blocked(s.view(torch.uint8))
+    else:
+        raise KeyError(name)
+
+
+def cpu_baseline(name, steps, warmup, sample_rows):
+    import torch
+
+    from transformer_nuggets_b200.workloads import CONFIGS, make_input
+
+    cfg = CONFIGS[name]
+    x = make_input(name, "cpu", rows=sample_rows)
+    for _ in range(warmup):
+        cpu_reference_pass(name, x)
+    times = []
+    for _ in range(steps):
+        t = time.perf_counter()
+        cpu_reference_pass(name, x)
+        times.append(time.perf_counter() - t)
+    sec = sum(times) / len(times)
+    nbytes = cfg.algo_bytes_per_elem * x.numel()
+    return {
+        "value": nbytes / sec / 1e9,
+        "unit": UNIT,
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"{sample_rows} of {cfg.rows} rows x {cfg.cols} cols ({name}), {steps} timed passes, "
+                  f"{sec * 1e3:.1f} ms per pass, PyTorch CPU eager ops of the reference path",
+    }, sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from transformer_nuggets_b200.workloads import CONFIGS
+
+    cfg = CONFIGS[args.workload]
+    sample_rows = max(128, cfg.rows // 32)
+    base, sec = cpu_baseline(args.workload, args.steps, args.warmup, sample_rows)
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, args.gpus, "none (CPU)"),
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(name, n_gpus, exchange, rows=None):
+    import dataclasses
+
+    from transformer_nuggets_b200.workloads import CONFIGS
+
+    cfg = CONFIGS[name]
+    if rows:
+        cfg = dataclasses.replace(cfg, rows=rows)
+    return {
+        "workload": f"{name}: {cfg.description}; bf16 {cfg.rows}x{cfg.cols}",
+        "rows": cfg.rows, "cols": cfg.cols, "shards": n_gpus, "exchange": exchange,
+        "algorithmic_bytes_per_element": cfg.algo_bytes_per_elem,
+        "l2": "inputs larger than L2 (each rank's shard is >= 256 MiB against 126 MB of L2)",
+    }
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import transformer_nuggets_b200 as tn
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.dist.sharded import plan_row_shards, sharded_dynamic_scaled_quant
+    from transformer_nuggets_b200.workloads import CONFIGS, make_input
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    cfg = CONFIGS[HEADLINE]
+    if args.rows:  # smaller same-shape case for profiler captures
+        import dataclasses
+
+        cfg = dataclasses.replace(cfg, rows=args.rows)
+    s, e = plan_row_shards(cfg.rows, world)[rank]
+    x = make_input(HEADLINE, dev, rows=e - s, row_offset=rank)
+    out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    n_local = x.numel()
+    total_elems = cfg.rows * cfg.cols
+    exchange = None
+    exchange_name = "single GPU"
+    if world > 1:
+        if args.exchange == "peer":
+            from transformer_nuggets_b200.dist.exchange import PeerAmaxExchange
+
+            exchange = PeerAmaxExchange(None)
+            exchange_name = "NVLink peer stores (8-byte word per rank), fused into the amax and cast kernels"
+        else:
+            exchange_name = "NCCL all-reduce(MAX) of one fp32"
+
+    def step():
+        sharded_dynamic_scaled_quant(x, None, exchange=exchange, out=out)
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_load0 = time.perf_counter()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_step = ms_total / args.steps
+    value = cfg.algo_bytes_per_elem * total_elems / (ms_step * 1e-3) / 1e9
+    launches = 2 * args.steps
+    if exchange is not None and exchange.status() != 0:
+        raise SystemExit("a bounded wait of the amax exchange expired during the timed steps")
+
+    if args.profile:  # profiler capture run: the timed steps only
+        if rank == 0:
+            if sampler:
+                sampler.stop(t_load0, time.perf_counter())
+            print(json.dumps({"profile_run": True, "rows": cfg.rows, "ms_per_step": ms_step, "value": value}))
+        if exchange is not None:
+            exchange.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- per-kernel durations of the same two kernels (CUDA events around each launch) ----
+    ws = _lib.workspace(dev)
+    stream = _lib.stream_ptr(dev)
+    amax = torch.empty(1, dtype=torch.float32, device=dev)
+    k_iters = max(args.steps, 20)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(k_iters)]
+    t_k0 = time.perf_counter()
+    reps = 0
+    while True:
+        for it in range(k_iters):
+            evs[it][0].record()
+            _lib.call("tnq_fp8_amax", x.data_ptr(), n_local, _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), amax.data_ptr(), stream)
+            evs[it][1].record()
+            _lib.call("tnq_fp8_scaled_cast", x.data_ptr(), out.data_ptr(), n_local, _lib.IN_BF16, _lib.FP8_E4M3,
+                      amax.data_ptr(), _lib.SCALE_IS_AMAX, 1, 0, 0, stream)
+            evs[it][2].record()
+        torch.cuda.synchronize()
+        reps += 1
+        if time.perf_counter() - t_k0 > 1.2 or reps >= 50:
+            break
+    t_load1 = time.perf_counter()
+    clocks = sampler.stop(t_load0, t_load1) if sampler else None
+    amax_ms = statistics.mean(ev[0].elapsed_time(ev[1]) for ev in evs)
+    cast_ms = statistics.mean(ev[1].elapsed_time(ev[2]) for ev in evs)
+    peak, peak_kind = measured_peak_gbs()
+    cast_bytes = 3.0 * n_local
+    amax_bytes = 2.0 * n_local
+    cast_gbs = cast_bytes / (cast_ms * 1e-3) / 1e9
+    amax_gbs = amax_bytes / (amax_ms * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "k_cast (bf16 -> e4m3 saturated cast, 2 B read + 1 B written per element)",
+        "achieved": cast_gbs, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s", "frac": cast_gbs / peak,
+        "traffic": None, "launch_ms": cast_ms, "algorithmic_bytes_per_launch": cast_bytes,
+        "other_kernels": {"k_amax": {"achieved": amax_gbs, "frac": amax_gbs / peak, "launch_ms": amax_ms,
+                                     "algorithmic_bytes_per_launch": amax_bytes}},
+    }
+    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_path):
+        try:
+            with open(traffic_path) as f:
+                tr = json.load(f)
+            per_elem = tr["k_cast"]["dram_bytes_per_element"]
+            roofline["traffic"] = per_elem * n_local
+            roofline["traffic_source"] = tr["k_cast"]["source"]
+        except Exception:
+            pass
+
+    # ---- end to end: pinned host buffers in, pinned host buffers out, every step ----
+    host_in = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+    host_in.copy_(x)
+    host_out = torch.empty(out.shape, dtype=torch.uint8, pin_memory=True)
+    dev_in = torch.empty_like(x)
+
+    def e2e_step():
+        dev_in.copy_(host_in, non_blocking=True)
+        q, _ = sharded_dynamic_scaled_quant(dev_in, None, exchange=exchange, out=out)
+        host_out.copy_(q.view(torch.uint8), non_blocking=True)
+
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+    e2e = {
+        "value": cfg.algo_bytes_per_elem * total_elems / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+        "ms_per_step": e2e_ms, "h2d_bytes_per_step": x.numel() * x.element_size(), "d2h_bytes_per_step": out.numel(),
+        "api": "transformer_nuggets_b200.dist.sharded.sharded_dynamic_scaled_quant on pinned host rows",
+    }
+    launches += 0  # the e2e and per-kernel passes are outside the timed region
+
+    extras = None
+    if world == 1 and not args.no_extras:
+        extras = other_workloads(dev, peak)
+
+    base = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        base, _ = cpu_baseline(HEADLINE, 3, 1, cfg.rows // 8)
+
+    if exchange is not None:
+        exchange.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(HEADLINE, world, exchange_name, cfg.rows),
+        "frac_of_measured_peak_per_gpu": value / world / peak, "frac_of_nominal_8000_per_gpu": value / world / 8000.0,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+    }
+    if base is not None:
+        line["cpu_baseline"] = base
+    if extras is not None:
+        line["other_workloads"] = extras
+    print(json.dumps(line))
+
+
+def other_workloads(dev, peak):
+    """Single-GPU configurations, timed the same way (CUDA events, cold L2 by rotating
+    buffer sets larger than L2 together).  Reported beside the headline."""
+    import torch
+
+    import transformer_nuggets_b200 as tn
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import CONFIGS, make_input
+
+    res = {}
+
+    def timed(fn, sets, iters=30, warm=5):
+        for i in range(warm):
+            fn(sets[i % len(sets)])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(sets[i % len(sets)])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    ws = _lib.workspace(dev)
+    stream = _lib.stream_ptr(dev)
+
+    def report(name, ms, note, bytes_per_elem=None):
+        cfg = CONFIGS[name]
+        bpe = cfg.algo_bytes_per_elem if bytes_per_elem is None else bytes_per_elem
+        gbs = bpe * cfg.rows * cfg.cols / (ms * 1e-3) / 1e9
+        return {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+                "algorithmic_bytes_per_element": bpe, "note": note}
+
+    # per-tensor dynamic e4m3, 4096 x 4096: 8 rotating buffer sets (8 x 48 MiB > L2)
+    base = make_input("fp8_tensor", dev)
+    sets = [(base.clone(), torch.empty_like(base, dtype=torch.float8_e4m3fn)) for _ in range(8)]
+
+    def f1(s):
+        _lib.call("tnq_fp8_dynamic_cast", s[0].data_ptr(), s[1].data_ptr(), s[0].numel(), _lib.IN_BF16, _lib.FP8_E4M3,
+                  ws.data_ptr(), 0, stream)
+
+    res["fp8_tensor"] = report("fp8_tensor", timed(f1, sets, 64, 16), "cold L2: 8 rotating buffer sets")
+    res["fp8_tensor_hot_l2"] = report("fp8_tensor", timed(f1, sets[:1], 64, 16), "hot L2: one buffer set")
+    del sets
+
+    x = make_input("fp8_rowwise", dev)
+    q43, q52 = torch.empty_like(x, dtype=torch.float8_e4m3fn), torch.empty_like(x, dtype=torch.float8_e5m2)
+    s43 = torch.empty(x.shape[0], 1, dtype=torch.float32, device=dev)
+    s52 = torch.empty_like(s43)
+
+    def f2(_):
+        _lib.call("tnq_fp8_rowwise", x.data_ptr(), x.shape[0], x.shape[1], _lib.IN_BF16, q43.data_ptr(), s43.data_ptr(),
+                  q52.data_ptr(), s52.data_ptr(), stream)
+
+    res["fp8_rowwise"] = report("fp8_rowwise", timed(f2, [None]), "input 256 MiB > L2")
+    del x, q43, q52
+
+    x = make_input("mxfp8", dev)
+    rows, cols = x.shape
+    qr = torch.empty(rows, cols, dtype=torch.uint8, device=dev)
+    qc = torch.empty(cols, rows, dtype=torch.uint8, device=dev)
+    sr = torch.empty(512 * (rows // 128) * ((cols // 32 + 3) // 4), dtype=torch.uint8, device=dev)
+    sc = torch.empty(512 * ((cols + 127) // 128) * ((rows // 32 + 3) // 4), dtype=torch.uint8, device=dev)
+    status = ws.data_ptr() + 4 * _lib.WS_STATUS_WORD
+
+    def f3(_):
+        _lib.call("tnq_mxfp8_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, qr.data_ptr(), sr.data_ptr(), qc.data_ptr(),
+                  sc.data_ptr(), _lib.E8M0_CEIL, _lib.SCALES_SWIZZLED, status, stream)
+
+    def f3r(_):
+        _lib.call("tnq_mxfp8_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, qr.data_ptr(), sr.data_ptr(), 0,
+                  0, _lib.E8M0_CEIL, _lib.SCALES_SWIZZLED, status, stream)
+
+    # input 112 MiB + outputs 114 MiB per call: rotate nothing, the footprint alone exceeds L2
+    res["mxfp8"] = report("mxfp8", timed(f3, [None]), "row + column outputs, swizzled scales; footprint 226 MiB > L2")
+    res["mxfp8_rowwise_only"] = report("mxfp8", timed(f3r, [None]), "row-wise output only", 2.0 + 1.0 + 1.0 / 32)
+    del x, qr, qc
+
+    x = make_input("nvfp4", dev)
+    rows, cols = x.shape
+    packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev)
+    sf = torch.empty(512 * (rows // 128) * (cols // 64), dtype=torch.uint8, device=dev)
+    gs = torch.empty(1, dtype=torch.float32, device=dev)
+    amax_ptr = ws.data_ptr() + 4 * _lib.WS_AMAX_WORD
+
+    def f4(_):
+        _lib.call("tnq_fp8_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), 0, stream)
+        _lib.call("tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, amax_ptr, packed.data_ptr(), sf.data_ptr(),
+                  _lib.SCALES_SWIZZLED, gs.data_ptr(), status, stream)
+
+    def f4s(_):
+        _lib.call("tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, amax_ptr, packed.data_ptr(), sf.data_ptr(),
+                  _lib.SCALES_SWIZZLED, gs.data_ptr(), status, stream)
+
+    res["nvfp4"] = report("nvfp4", timed(f4, [None], 20, 4), "dynamic global scale (amax pass + quantize pass)")
+    res["nvfp4_given_global_amax"] = report("nvfp4", timed(f4s, [None], 20, 4), "global amax supplied", 2.5625)
+    st = int(ws[_lib.WS_STATUS_WORD].item())
+    if st != 0:
+        raise SystemExit(f"device status word {st}: a bounded wait expired in a tile kernel")
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=HEADLINE)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the other single-GPU configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--rows", type=int, default=0, help="override the headline workload's row count (profiling)")
+    ap.add_argument("--profile", action="store_true", help="run only warm-up and timed steps (for ncu captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

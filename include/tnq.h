@@ -1,0 +1,161 @@
+/*
+ * tnq - scaled-quantization casts for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libtnq.so.  Plain pointers and sizes only; every pointer is a CUDA
+ * device pointer unless a comment says "host".  Except for the tnq_exchange_*
+ * set-up functions, no function allocates, frees or synchronises; all work is
+ * enqueued on `stream`.  Each function returns a tnq_status; on anything but
+ * TNQ_OK nothing was launched.
+ *
+ * Each entry point names the function of drisspg/transformer_nuggets whose
+ * device work it replaces (path:line within that project).
+ */
+#ifndef TNQ_H_
+#define TNQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tnq_stream_t;
+
+typedef enum {
+  TNQ_OK = 0,
+  TNQ_EINVAL = 1,       /* null pointer, negative size, unknown enum          */
+  TNQ_EALIGN = 2,       /* pointer or row pitch not 16-byte aligned            */
+  TNQ_ESHAPE = 3,       /* shape not a multiple of the block size              */
+  TNQ_EUNSUPPORTED = 4, /* dtype / size combination not built                  */
+  TNQ_ECUDA = 5,        /* a CUDA runtime call failed (see tnq_last_cuda_error)*/
+  TNQ_ETIMEOUT = 6      /* a bounded device-side wait gave up (status word)    */
+} tnq_status;
+
+typedef enum { TNQ_IN_BF16 = 0, TNQ_IN_F32 = 1 } tnq_in_dtype;
+typedef enum { TNQ_FP8_E4M3 = 0, TNQ_FP8_E5M2 = 1 } tnq_fp8_dtype;
+typedef enum { TNQ_E8M0_CEIL = 0, TNQ_E8M0_FLOOR = 1 } tnq_e8m0_mode;
+typedef enum { TNQ_SCALES_RAW = 0, TNQ_SCALES_SWIZZLED = 1 } tnq_scale_layout;
+typedef enum { TNQ_SCALE_IS_SCALE = 0, TNQ_SCALE_IS_AMAX = 1 } tnq_scale_source;
+
+/* Caller-owned scratch for the per-tensor reductions: TNQ_WORKSPACE_BYTES
+ * bytes, 256-byte aligned, zero-filled ONCE after allocation.  The kernels
+ * leave it ready for the next call.  Two calls that share a workspace must be
+ * ordered (same stream); use one workspace per concurrent stream.
+ * Layout (uint32 words): [0] ticket  [1] amax as fp32 bits  [2] scale (fp32)
+ * [3] device status  [16..] per-CTA partial maxima. */
+#define TNQ_WORKSPACE_BYTES 16384
+#define TNQ_WS_AMAX_WORD 1
+#define TNQ_WS_SCALE_WORD 2
+#define TNQ_WS_STATUS_WORD 3
+
+const char* tnq_status_str(int status);
+/* cudaError_t of the most recent failing runtime call on this thread (0 if none). */
+int tnq_last_cuda_error(void);
+/* Library ABI version; bumped when a signature changes. */
+int tnq_abi_version(void);
+
+/* amax = max|x| over n elements, written as fp32 to ws word TNQ_WS_AMAX_WORD and,
+ * if non-null, to *amax_out; ws word TNQ_WS_SCALE_WORD receives
+ * fp8_max(out_dtype) / max(amax, 1e-12).
+ * Replaces pass one of `dynamic_scaled_cast` (fp8/scaled_quant.py:115-119). */
+int tnq_fp8_amax(const void* x, int64_t n, int in_dtype, int out_dtype, void* workspace,
+                 float* amax_out, tnq_stream_t stream);
+
+/* out[i] = fp8(x[i] * s), s = *scale (TNQ_SCALE_IS_SCALE) or
+ * fp8_max / max(*scale, 1e-12) (TNQ_SCALE_IS_AMAX).  saturated != 0 clamps to
+ * +-fp8_max first; saturated == 0 overflows to NaN (e4m3) / inf (e5m2) exactly as
+ * a non-saturating RNE cast does.  If abs_max_inout is non-null it becomes
+ * max(*abs_max_inout, max|x|) and `workspace` must be given.
+ * Replaces `scaled_cast` / `scaled_quant` (fp8/scaled_quant.py:6-32, 35-75) with
+ * the overflow semantics of `eager_scaled_quant` (:78-102). */
+int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                        const float* scale, int scale_source, int saturated,
+                        float* abs_max_inout, void* workspace, tnq_stream_t stream);
+
+/* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast, as two dependent
+ * launches (the second re-reads x, from L2 when x fits there).  *scale_out
+ * (nullable) receives the scale.
+ * Replaces `dynamic_scaled_cast` / `dynamic_scaled_quant` (fp8/scaled_quant.py:108-169). */
+int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                         void* workspace, float* scale_out, tnq_stream_t stream);
+
+/* Row-wise dynamic cast of x[rows, cols] (row-major, contiguous).  For each
+ * requested output (a null q pointer skips it) q[r, :] = sat_fp8(x[r, :] * s_r),
+ * s_r = fp8_max / max(amax_r, 1e-12) written to scale[r] (fp32, [rows]).
+ * The reference has no row-wise cast; the scale shape is the [M, 1] fp32 contract
+ * of fp8/fp8_matmul.py:50-61 and the arithmetic is fp8/scaled_quant.py:132-135 per row. */
+int tnq_fp8_rowwise(const void* x, int64_t rows, int64_t cols, int in_dtype, void* q_e4m3,
+                    float* scale_e4m3, void* q_e5m2, float* scale_e5m2, tnq_stream_t stream);
+
+/* MXFP8: 32-element blocks, E8M0 scale byte = exponent + 127, e4m3 payload.
+ * Row-wise outputs (blocks along cols): q_row[rows, cols], sf_row for the
+ * [rows, cols/32] scale matrix.  Column-wise outputs (blocks along rows, i.e. the
+ * row-wise quantisation of x^T): q_col[cols, rows], sf_col for [cols, rows/32].
+ * Either pair may be null.  scale_layout RAW = row-major scale matrix;
+ * SWIZZLED = the 128x4 layout of `to_blocked`, whose buffers hold
+ * 512*ceil(H/128)*ceil(W/4) bytes; the kernel writes every byte of them (padding
+ * positions become 0).  Requires cols % 32 == 0 for the row-wise pair, rows % 32 == 0
+ * for the column-wise pair, bf16 input.  `status` (nullable) is a device word that
+ * receives TNQ_ETIMEOUT if a bounded wait inside the kernel gives up.
+ * Replaces `quantize_mxfp8_tensor` (cute/mxfp8_tma.py:497-504) and, when
+ * swizzled, the following `to_blocked` (mx/to_blocked.py:10-42). */
+int tnq_mxfp8_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype, void* q_row,
+                       void* sf_row, void* q_col, void* sf_col, int e8m0_mode, int scale_layout,
+                       uint32_t* status, tnq_stream_t stream);
+
+/* NVFP4: 16-element blocks along cols, e4m3 block scales, two e2m1 codes per byte
+ * (low nibble first), fp32 global scale.  *global_amax is max|x| of the whole
+ * tensor (device fp32, e.g. ws word TNQ_WS_AMAX_WORD after tnq_fp8_amax).
+ * packed[rows, cols/2]; sf for the [rows, cols/16] scale matrix in scale_layout;
+ * *global_scale_out (nullable) = max(amax, 1e-12) / 2688, the decode-direction scale.
+ * Requires cols % 16 == 0, bf16 input.  `status` as for tnq_mxfp8_quantize.
+ * The reference has no NVFP4 quantizer; the outputs follow its storage contract
+ * (cute/nvfp4_tma.py:941-964, :527-547). */
+int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype,
+                       const float* global_amax, void* packed, void* sf, int scale_layout,
+                       float* global_scale_out, uint32_t* status, tnq_stream_t stream);
+
+/* codes[rows, cols] (one e2m1 code 0..15 per byte) -> packed[rows, cols/2] with
+ * byte = code[2i] | code[2i+1] << 4.  Requires cols % 16 == 0.
+ * Replaces `pack_nvfp4_codes` (cute/nvfp4_tma.py:941-943). */
+int tnq_pack_fp4_codes(const void* codes, int64_t rows, int64_t cols, void* packed,
+                       tnq_stream_t stream);
+
+/* One-byte scale matrix in[rows, cols] (row-major) -> 128x4-swizzled flat buffer of
+ * 512*ceil(rows/128)*ceil(cols/4) bytes, padding zero-filled by the kernel.
+ * Replaces `to_blocked` (mx/to_blocked.py:10-42) and `ToBlocked.kernel`
+ * (cute/to_blocked.py:26-73). */
+int tnq_to_blocked(const void* in, int64_t rows, int64_t cols, void* out, tnq_stream_t stream);
+
+/* ---- row-sharded per-tensor cast: one process per GPU, amax exchanged by peer stores.
+ * The reference has no multi-device cast; its collective precedent is the peer-load
+ * all-reduce over symmetric memory of cute/symmetric_memory.py:20-79. ---- */
+
+/* Set-up, once per process group (these allocate / synchronise).  create: a 4 KiB
+ * zeroed slot buffer on the current device and its 64-byte CUDA IPC handle (host
+ * memory).  open: map a peer process's buffer from its handle (enables peer access).
+ * close / destroy: undo open / create.  status: synchronising read of the buffer's
+ * status word into *host_status (host memory); non-zero = a bounded wait expired. */
+int tnq_exchange_create(void** local_slots, unsigned char ipc_handle[64]);
+int tnq_exchange_open(const unsigned char ipc_handle[64], void** peer_slots);
+int tnq_exchange_close(void* peer_slots);
+int tnq_exchange_destroy(void* local_slots);
+int tnq_exchange_status(const void* local_slots, uint32_t* host_status);
+
+/* Cast this rank's n elements with the scale of the whole sharded tensor:
+ * local amax -> one 8-byte store (sequence number, amax) into every rank's slot
+ * buffer -> the cast kernel waits (bounded, about 1 s) until its OWN buffer holds all
+ * world_size words of sequence `seq`, takes their MAX and casts saturated.
+ * slot_buffers is a HOST array of world_size device pointers (slot_buffers[rank] is
+ * this rank's own buffer, the others come from tnq_exchange_open).  seq must be
+ * non-zero, identical on all ranks for the same call and different from the previous
+ * two calls' (increment it).  *amax_out (nullable) receives the global amax.
+ * world_size <= 16. */
+int tnq_fp8_sharded_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                         void* workspace, void* const* slot_buffers, int world_size, int rank,
+                         uint32_t seq, float* amax_out, tnq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TNQ_H_ */

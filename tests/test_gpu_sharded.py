@@ -1,0 +1,113 @@
+"""Row-sharded per-tensor cast: the shards together equal the single-device result
+bit for bit.  On one GPU the ranks are emulated one after another through the same
+C-ABI calls; with two or more GPUs a real NCCL group of child processes runs too."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+import oracle
+import transformer_nuggets_b200 as tn
+from conftest import as_u8
+from transformer_nuggets_b200 import _lib
+from transformer_nuggets_b200.dist.sharded import plan_row_shards, sharded_dynamic_scaled_quant
+from transformer_nuggets_b200.workloads import make_input
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def emulate_ranks(x, world):
+    """local amax per shard -> MAX on the host side of the test -> cast per shard."""
+    plan = plan_row_shards(x.shape[0], world)
+    ws = _lib.workspace(x.device)
+    stream = _lib.stream_ptr(x.device)
+    amaxes = []
+    for s, e in plan:
+        a = torch.zeros(1, dtype=torch.float32, device=DEV)
+        sh = x[s:e]
+        _lib.call("tnq_fp8_amax", sh.data_ptr(), sh.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), a.data_ptr(), stream)
+        amaxes.append(a)
+    g = torch.stack(amaxes).max().reshape(1).contiguous()
+    outs = []
+    for s, e in plan:
+        sh = x[s:e]
+        o = torch.empty_like(sh, dtype=torch.float8_e4m3fn)
+        _lib.call("tnq_fp8_scaled_cast", sh.data_ptr(), o.data_ptr(), sh.numel(), _lib.IN_BF16, _lib.FP8_E4M3,
+                  g.data_ptr(), _lib.SCALE_IS_AMAX, 1, 0, 0, stream)
+        outs.append(o)
+    return torch.cat(outs), g
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_emulated_shards_equal_unsharded_small(world):
+    x = make_input("fp8_sharded", "cpu", rows=2048, cols=1024)
+    want, wscale = oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)
+    got, amax = emulate_ranks(x.to(DEV), world)
+    assert torch.equal(torch.tensor(448.0) / amax.cpu(), wscale)
+    assert torch.equal(as_u8(got).cpu(), as_u8(want))
+
+
+def test_config_sharded_full_size():
+    """131072 x 8192 (2 GiB): 8 emulated shards == one device, bit for bit; the
+    scale equals 448 / amax; sampled rows against the oracle."""
+    x = make_input("fp8_sharded", DEV)
+    full, scale = tn.dynamic_scaled_quant_with_scale(x)
+    got, amax = emulate_ranks(x, 8)
+    assert torch.equal(as_u8(got), as_u8(full))
+    assert amax.item() == x.abs().max().float().item()
+    assert torch.equal(scale.cpu(), torch.tensor([448.0]) / amax.cpu())
+    one, amax1 = sharded_dynamic_scaled_quant(x)  # world size 1 through the product entry point
+    assert torch.equal(as_u8(one), as_u8(full)) and torch.equal(amax1, amax)
+    rows = torch.arange(0, 131072, 997, device=DEV)
+    xs = x[rows].cpu()
+    want = oracle.fp8_scaled_quant(xs, scale.cpu(), torch.zeros(1), torch.float8_e4m3fn, True)
+    assert torch.equal(as_u8(full[rows]).cpu(), as_u8(want))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _nccl_rank(rank, world, port, results):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        x = make_input("fp8_sharded", "cpu", rows=4096, cols=1024)
+        want, wscale = oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)
+        s, e = plan_row_shards(x.shape[0], world)[rank]
+        ok = True
+        for exch in ("nccl", "peer"):
+            exchange = None
+            if exch == "peer":
+                from transformer_nuggets_b200.dist.exchange import PeerAmaxExchange
+
+                exchange = PeerAmaxExchange(None)
+            for _ in range(3):  # repeated calls reuse the exchange slots
+                q, amax = sharded_dynamic_scaled_quant(x[s:e].cuda(), None, exchange=exchange)
+                torch.cuda.synchronize()
+                ok = ok and torch.equal(torch.tensor(448.0) / amax.cpu(), wscale)
+                ok = ok and torch.equal(as_u8(q).cpu(), as_u8(want[s:e]))
+            if exchange is not None:
+                ok = ok and exchange.status() == 0
+                exchange.close()
+        results[rank] = 1 if ok else 0
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_nccl_and_peer_exchange_ranks():
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 8)
+    results = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_nccl_rank, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {r: 1 for r in range(world)}

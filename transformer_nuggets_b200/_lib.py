@@ -1,0 +1,124 @@
+"""ctypes binding of ``libtnq.so`` - the only route from Python to the kernels.
+
+There is no CPU path behind these functions: if the library is missing or an
+argument is not a CUDA tensor the call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libtnq.so")
+
+TNQ_OK = 0
+STATUS_NAMES = {1: "EINVAL", 2: "EALIGN", 3: "ESHAPE", 4: "EUNSUPPORTED", 5: "ECUDA", 6: "ETIMEOUT"}
+IN_BF16, IN_F32 = 0, 1
+FP8_E4M3, FP8_E5M2 = 0, 1
+E8M0_CEIL, E8M0_FLOOR = 0, 1
+SCALES_RAW, SCALES_SWIZZLED = 0, 1
+SCALE_IS_SCALE, SCALE_IS_AMAX = 0, 1
+WORKSPACE_BYTES = 16384
+WS_AMAX_WORD, WS_SCALE_WORD, WS_STATUS_WORD = 1, 2, 3
+
+IN_DTYPES = {torch.bfloat16: IN_BF16, torch.float32: IN_F32}
+FP8_DTYPES = {torch.float8_e4m3fn: FP8_E4M3, torch.float8_e5m2: FP8_E5M2}
+
+_p, _i64, _i = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+
+# name -> argument types (all return int unless noted)
+SIGNATURES = {
+    "tnq_fp8_amax": [_p, _i64, _i, _i, _p, _p, _p],
+    "tnq_fp8_scaled_cast": [_p, _p, _i64, _i, _i, _p, _i, _i, _p, _p, _p],
+    "tnq_fp8_dynamic_cast": [_p, _p, _i64, _i, _i, _p, _p, _p],
+    "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p],
+    "tnq_mxfp8_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _p],
+    "tnq_nvfp4_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p, _p],
+    "tnq_pack_fp4_codes": [_p, _i64, _i64, _p, _p],
+    "tnq_to_blocked": [_p, _i64, _i64, _p, _p],
+    "tnq_exchange_create": [_p, _p],
+    "tnq_exchange_open": [_p, _p],
+    "tnq_exchange_close": [_p],
+    "tnq_exchange_destroy": [_p],
+    "tnq_exchange_status": [_p, _p],
+    "tnq_fp8_sharded_cast": [_p, _p, _i64, _i, _i, _p, _p, _i, _i, ctypes.c_uint32, _p, _p],
+    "tnq_last_cuda_error": [],
+    "tnq_abi_version": [],
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+class TnqError(RuntimeError):
+    def __init__(self, fn, status, detail=""):
+        self.status = status
+        super().__init__(f"{fn} failed: {STATUS_NAMES.get(status, status)} {detail}".strip())
+
+
+def load():
+    """Load (once) and return the ctypes handle.  Raises if the library is absent:
+    build it with ``python -m transformer_nuggets_b200.build``."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise ImportError(
+                    f"{LIB_PATH} not found. The cast kernels are CUDA only and have no fallback; "
+                    "build them with `python -m transformer_nuggets_b200.build`."
+                )
+            lib = ctypes.CDLL(LIB_PATH)
+            for name, argtypes in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.argtypes = argtypes
+                fn.restype = _i
+            lib.tnq_status_str.argtypes = [_i]
+            lib.tnq_status_str.restype = ctypes.c_char_p
+            _lib = lib
+    return _lib
+
+
+def call(name, *args):
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != TNQ_OK:
+        detail = lib.tnq_status_str(rc).decode()
+        if rc == 5:
+            detail += f" (cudaError {lib.tnq_last_cuda_error()})"
+        raise TnqError(name, rc, detail)
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def require_cuda(t: torch.Tensor, what: str):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{what} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{what} must be a CUDA tensor: the cast kernels have no CPU path")
+
+
+_workspaces: dict = {}
+
+
+def workspace(device) -> torch.Tensor:
+    """Zero-initialised per-(device, stream) scratch for the tensor-wide reductions."""
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(WORKSPACE_BYTES // 4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _workspaces[key] = ws
+    return ws

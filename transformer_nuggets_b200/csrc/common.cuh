@@ -1,0 +1,267 @@
+// Device helpers shared by the cast kernels (sm_100a only).
+//
+// Arithmetic contract: every product / quotient is a single IEEE fp32 operation
+// (__fmul_rn / __fdiv_rn, never contracted into an FMA, no flush-to-zero), the
+// fp8 / fp4 conversion is the hardware round-to-nearest-even `cvt`, and |x| maxima
+// are taken on the integer view of the input (same order as the float order for
+// every non-NaN value; any NaN compares above infinity and therefore wins).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/tnq.h"
+
+namespace tnq {
+
+constexpr float kAmaxEps = 1e-12f;
+
+// ------------------------------------------------------------------ loads / stores
+struct alignas(32) Vec32B {
+  uint32_t w[8];
+};
+
+__device__ __forceinline__ uint4 ldg128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// 256-bit global load (one instruction per 32 bytes; new with sm_100).
+__device__ __forceinline__ Vec32B ldg256(const void* p) {
+  Vec32B v;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                 "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void stg128(void* p, uint4 v) {
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void stg64(void* p, uint2 v) {
+  asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void stg32(void* p, uint32_t v) {
+  asm volatile("st.global.L1::no_allocate.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// ------------------------------------------------------------------ bf16 pairs
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// max of |.| over packed bf16 pairs, on the 15-bit magnitude
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t m, uint32_t w) {
+  return __vmaxu2(m, w & 0x7fff7fffu);
+}
+__device__ __forceinline__ uint32_t fold_u16x2(uint32_t m) { return max(m & 0xffffu, m >> 16); }
+__device__ __forceinline__ float bf16bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+// ------------------------------------------------------------------ fp8 conversion
+template <int OUT>
+struct Fp8Traits;
+template <>
+struct Fp8Traits<TNQ_FP8_E4M3> {
+  static constexpr float kMax = 448.0f;
+  static constexpr uint32_t kNanAdd = 0x01010101u;  // (b & 0x7f) == 0x7f  <=> NaN
+  static constexpr uint32_t kOverflowByte = 0x7f;   // non-saturating overflow -> NaN
+};
+template <>
+struct Fp8Traits<TNQ_FP8_E5M2> {
+  static constexpr float kMax = 57344.0f;
+  static constexpr uint32_t kNanAdd = 0x04040404u;  // (b & 0x7f) >= 0x7c  <=> inf / NaN
+  static constexpr uint32_t kOverflowByte = 0x7c;   // non-saturating overflow -> inf
+};
+
+template <int OUT>
+__device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
+  uint16_t r;
+  if constexpr (OUT == TNQ_FP8_E4M3) {
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+template <int OUT>
+__device__ __forceinline__ uint32_t cvt_fp8x4(float a, float b, float c, float d) {
+  return cvt_fp8x2<OUT>(a, b) | (cvt_fp8x2<OUT>(c, d) << 16);
+}
+
+// Exact scalar cast with the corner cases of the CPU path the results are checked
+// against: NaN keeps a sign (that of x if x is NaN, else that of a NaN scale, else
+// negative - the default NaN an x86 multiply produces for inf * 0); without
+// saturation, overflow becomes NaN (e4m3fn, |y| rounds above 448, i.e. |y| > 464)
+// or infinity (e5m2, |y| >= 61440).
+template <int OUT, bool SAT>
+__device__ __noinline__ uint32_t fp8_scalar_exact(float x, float scale) {
+  const float y = __fmul_rn(x, scale);
+  if (y != y) {
+    uint32_t sign = 1u;
+    if (x != x) sign = __float_as_uint(x) >> 31;
+    else if (scale != scale) sign = __float_as_uint(scale) >> 31;
+    return 0x7fu | (sign << 7);
+  }
+  uint32_t b = cvt_fp8x2<OUT>(y, 0.0f) & 0xffu;
+  if constexpr (!SAT) {
+    const float a = fabsf(y);
+    const bool over = (OUT == TNQ_FP8_E4M3) ? (a > 464.0f) : (a >= 61440.0f);
+    if (over) b = (b & 0x80u) | Fp8Traits<OUT>::kOverflowByte;
+  }
+  return b;
+}
+
+// Four scaled values -> four fp8 bytes.  The fast path is two hardware cvt; a word
+// that contains a NaN byte (or, without saturation, an overflowing value) is redone
+// element by element.  x0..x3 are the unscaled inputs.
+template <int OUT, bool SAT>
+__device__ __forceinline__ uint32_t quant4(float x0, float x1, float x2, float x3, float s) {
+  const float y0 = __fmul_rn(x0, s), y1 = __fmul_rn(x1, s), y2 = __fmul_rn(x2, s), y3 = __fmul_rn(x3, s);
+  uint32_t w = cvt_fp8x4<OUT>(y0, y1, y2, y3);
+  bool redo = (((w & 0x7f7f7f7fu) + Fp8Traits<OUT>::kNanAdd) & 0x80808080u) != 0u;
+  if constexpr (!SAT) {
+    const float m = fmaxf(fmaxf(fabsf(y0), fabsf(y1)), fmaxf(fabsf(y2), fabsf(y3)));
+    redo = redo || ((OUT == TNQ_FP8_E4M3) ? (m > 464.0f) : (m >= 61440.0f));
+  }
+  if (__builtin_expect(redo, 0)) {
+    w = fp8_scalar_exact<OUT, SAT>(x0, s) | (fp8_scalar_exact<OUT, SAT>(x1, s) << 8) |
+        (fp8_scalar_exact<OUT, SAT>(x2, s) << 16) | (fp8_scalar_exact<OUT, SAT>(x3, s) << 24);
+  }
+  return w;
+}
+
+// 8 bf16 (one 16-byte vector) -> 8 fp8 bytes
+template <int OUT, bool SAT>
+__device__ __forceinline__ uint2 quant8_bf16(uint4 v, float s) {
+  uint2 o;
+  o.x = quant4<OUT, SAT>(bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y), s);
+  o.y = quant4<OUT, SAT>(bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w), s);
+  return o;
+}
+// 4 fp32 (one 16-byte vector) -> 4 fp8 bytes
+template <int OUT, bool SAT>
+__device__ __forceinline__ uint32_t quant4_f32(uint4 v, float s) {
+  return quant4<OUT, SAT>(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z),
+                          __uint_as_float(v.w), s);
+}
+
+// amax as fp32 -> scale = fp8_max / max(amax, 1e-12); a NaN amax stays NaN.
+__device__ __forceinline__ float scale_from_amax(float amax, float fp8_max) {
+  const float a = (amax != amax) ? amax : fmaxf(amax, kAmaxEps);
+  return __fdiv_rn(fp8_max, a);
+}
+
+// ------------------------------------------------------------------ reductions
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) { return __reduce_max_sync(0xffffffffu, v); }
+
+// max over a CTA of up to 1024 threads; every thread gets the result.
+__device__ __forceinline__ uint32_t block_max_u32(uint32_t v, uint32_t* smem32 /* >= 33 words */) {
+  v = warp_max_u32(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  __syncthreads();  // smem32 may still be read by a previous call
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  uint32_t r = (lane < nwarp) ? smem32[lane] : 0u;
+  return warp_max_u32(r);
+}
+
+// ------------------------------------------------------------------ scale swizzle
+// Byte offset of scale element (r, c) of an [H, W] scale matrix in the 128x4
+// ("SWIZZLE_32_4_4") layout; ncb = ceil(W / 4).
+__device__ __host__ __forceinline__ int64_t swizzled_offset(int64_t r, int64_t c, int64_t ncb) {
+  return ((r >> 7) * ncb + (c >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (c & 3);
+}
+
+// ------------------------------------------------------------------ mbarrier + bulk copy (TMA)
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait for a phase.  Returns false if the phase did not complete within
+// about one second; the caller must then flag the failure and leave.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 1000000000ull) return false;
+    }
+  }
+}
+// 1-D bulk copy global -> this CTA's shared memory; completion on `bar`.
+// Both addresses 16-byte aligned, bytes a multiple of 16.  Single destination CTA.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// 2-D tiled TMA load global -> this CTA's shared memory (x = innermost coordinate,
+// x * element size must be a multiple of 16 bytes).  Single destination CTA (the
+// kernels run with cluster size 1, so shared::cluster names this CTA's memory).
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int32_t x, int32_t y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// Programmatic dependent launch: wait for the grid this one depends on / let the
+// dependent grid start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+}  // namespace tnq
+
+// ------------------------------------------------------------------ host helpers
+namespace tnq_host {
+extern thread_local int g_last_cuda_error;
+int sm_count();  // SMs of the current device (cached per device)
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return TNQ_ECUDA;
+}
+inline int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TNQ_OK : cuda_fail(e);
+}
+}  // namespace tnq_host

@@ -1,0 +1,444 @@
+// Per-tensor FP8 casts: amax reduction, scaled cast (delayed scale, optional amax
+// side output) and the dynamic cast (amax -> scale -> saturated cast).
+//
+// All three are HBM streaming kernels.  Persistent grids (a multiple of the SM
+// count), grid-stride over 32-byte vectors, four independent 256-bit loads in
+// flight per thread, |x| maxima on the integer view, one warp `redux` + one shared
+// memory step per CTA, and a self-resetting ticket so that the last CTA to finish
+// combines the per-CTA partial maxima (no float atomics, no memset between calls).
+#include "common.cuh"
+
+namespace tnq {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kMaxPartials = (TNQ_WORKSPACE_BYTES - 64) / 4;
+
+struct Workspace {
+  uint32_t ticket;
+  uint32_t amax_bits;  // fp32 bit pattern
+  float scale;
+  uint32_t status;
+  uint32_t pad[12];
+  uint32_t partial[kMaxPartials];
+};
+
+// Cross-GPU amax exchange (row-sharded cast).  Every rank owns a slot array in its
+// own memory: slot[parity][r] holds rank r's amax for the call with that sequence
+// parity as one 64-bit word (sequence number << 32 | fp32 bits), so a single aligned
+// store publishes value and flag together.  A rank STORES its word into every peer's
+// array (plain peer stores over NVLink, one store per peer) and only ever
+// LOADS from its own memory.  Two parities suffice: a rank cannot publish call k+2
+// before every peer has consumed call k, because its own call k+1 needs theirs.
+constexpr int kMaxRanks = 16;
+constexpr int kSlotStride = 64;          // slots per parity in the buffer
+constexpr int kExchangeStatusWord = 512; // uint32 index of the status word (byte 2048)
+struct PeerSlots {
+  uint64_t* base[kMaxRanks];  // base[r] = rank r's slot buffer as seen from this GPU
+  int world;
+  int rank;
+  uint32_t seq;
+};
+struct ExchangeWait {
+  const uint64_t* slots;  // this rank's own buffer; nullptr = not used
+  int world;
+  uint32_t seq;
+  uint32_t* status;
+  float* amax_out;
+};
+
+// All ranks' amax for sequence `seq` from this GPU's own slots; bounded wait of about
+// one second.  Returns false on expiry.
+__device__ __forceinline__ bool exchange_collect(const ExchangeWait& ex, float* amax) {
+  const uint64_t* slot = ex.slots + (ex.seq & 1u) * kSlotStride;
+  uint32_t m = 0;
+  uint64_t t0 = 0;
+  for (int r = 0; r < ex.world; ++r) {
+    for (uint32_t it = 0;; ++it) {
+      uint64_t w;
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot + r) : "memory");
+      if ((uint32_t)(w >> 32) == ex.seq) {
+        m = max(m, (uint32_t)w);
+        break;
+      }
+      if ((it & 63u) == 63u) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 1000000000ull) return false;
+      }
+    }
+  }
+  *amax = __uint_as_float(m);
+  return true;
+}
+
+template <int IN>
+struct InTraits;
+template <>
+struct InTraits<TNQ_IN_BF16> {
+  static constexpr int kElemsPerVec = 16;  // per 32-byte vector
+  static constexpr int kElemBytes = 2;
+  __device__ static __forceinline__ uint32_t absmax(uint32_t m, const Vec32B& v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = absmax_bf16x2(m, v.w[i]);
+    return m;
+  }
+  __device__ static __forceinline__ uint32_t fold(uint32_t m) { return fold_u16x2(m) << 16; }  // -> fp32 bits
+  __device__ static __forceinline__ float load_scalar(const void* x, int64_t i) {
+    return bf16bits_to_f32(reinterpret_cast<const uint16_t*>(x)[i]);
+  }
+};
+template <>
+struct InTraits<TNQ_IN_F32> {
+  static constexpr int kElemsPerVec = 8;
+  static constexpr int kElemBytes = 4;
+  __device__ static __forceinline__ uint32_t absmax(uint32_t m, const Vec32B& v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = max(m, v.w[i] & 0x7fffffffu);
+    return m;
+  }
+  __device__ static __forceinline__ uint32_t fold(uint32_t m) { return m; }
+  __device__ static __forceinline__ float load_scalar(const void* x, int64_t i) {
+    return reinterpret_cast<const float*>(x)[i];
+  }
+};
+
+// 32 input bytes -> fp8 bytes, stored.
+template <int IN, int OUT, bool SAT>
+__device__ __forceinline__ void quant_store(const Vec32B& v, float s, uint8_t* out, int64_t vec_index) {
+  if constexpr (IN == TNQ_IN_BF16) {
+    const uint2 a = quant8_bf16<OUT, SAT>(make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), s);
+    const uint2 b = quant8_bf16<OUT, SAT>(make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]), s);
+    stg128(out + vec_index * 16, make_uint4(a.x, a.y, b.x, b.y));
+  } else {
+    uint2 o;
+    o.x = quant4_f32<OUT, SAT>(make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), s);
+    o.y = quant4_f32<OUT, SAT>(make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]), s);
+    stg64(out + vec_index * 8, o);
+  }
+}
+
+// Combine the CTA maxima: every CTA publishes its partial, takes a ticket, and the
+// CTA holding the last ticket folds all partials.  Returns true (in thread 0 of that
+// CTA only) with the tensor-wide maximum as fp32 bits.
+__device__ __forceinline__ bool grid_max(uint32_t cta_max_bits, Workspace* ws, uint32_t* smem32,
+                                         uint32_t* result_bits) {
+  __shared__ uint32_t s_last;
+  if (threadIdx.x == 0) {
+    ws->partial[blockIdx.x] = cta_max_bits;
+    __threadfence();
+    const uint32_t t = atomicInc(&ws->ticket, gridDim.x - 1);  // wraps to 0: ready for the next call
+    s_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_last) return false;
+  __threadfence();
+  uint32_t m = 0;
+  for (uint32_t i = threadIdx.x; i < gridDim.x; i += blockDim.x) m = max(m, __ldcg(&ws->partial[i]));
+  m = block_max_u32(m, smem32);
+  *result_bits = m;
+  return threadIdx.x == 0;
+}
+
+// ---------------------------------------------------------------- amax
+template <int IN, bool PUBLISH>
+__global__ void __launch_bounds__(kThreads)
+    k_amax(const uint8_t* __restrict__ x, int64_t n, Workspace* ws, float* amax_out, float* scale_out, float fp8_max,
+           PeerSlots peers) {
+  using T = InTraits<IN>;
+  __shared__ uint32_t smem32[33];
+  const int64_t nvec = n / T::kElemsPerVec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t m = 0;
+  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+    Vec32B v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = ldg256(x + (i + u * stride) * 32);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) m = T::absmax(m, v[u]);
+  }
+  for (; i < nvec; i += stride) m = T::absmax(m, ldg256(x + i * 32));
+  m = T::fold(m);
+  if (blockIdx.x == 0) {  // ragged tail, fewer than one vector
+    for (int64_t j = nvec * T::kElemsPerVec + threadIdx.x; j < n; j += blockDim.x)
+      m = max(m, __float_as_uint(T::load_scalar(x, j)) & 0x7fffffffu);
+  }
+  m = block_max_u32(m, smem32);
+  pdl_launch_dependents();
+  uint32_t total;
+  if (grid_max(m, ws, smem32, &total)) {
+    const float amax = __uint_as_float(total);
+    ws->amax_bits = total;
+    const float scale = scale_from_amax(amax, fp8_max);
+    ws->scale = scale;
+    if (amax_out) *amax_out = amax;
+    if (scale_out) *scale_out = scale;
+    if constexpr (PUBLISH) {
+      const uint64_t word = ((uint64_t)peers.seq << 32) | total;
+      const int idx = (int)(peers.seq & 1u) * kSlotStride + peers.rank;
+      for (int r = 0; r < peers.world; ++r)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peers.base[r] + idx), "l"(word) : "memory");
+    }
+  }
+}
+
+// ---------------------------------------------------------------- cast (optionally + amax)
+template <int IN, int OUT, bool SAT, bool AMAX>
+__global__ void __launch_bounds__(kThreads)
+    k_cast(const uint8_t* __restrict__ x, uint8_t* __restrict__ out, int64_t n, const float* scale_ptr,
+           int scale_source, float* abs_max_inout, Workspace* ws, ExchangeWait ex) {
+  using T = InTraits<IN>;
+  __shared__ uint32_t smem32[33];
+  pdl_wait();  // the scale may come from the preceding amax launch
+  float s;
+  if (ex.slots != nullptr) {  // amax of all ranks, read from this GPU's own slots
+    __shared__ float s_amax;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+      float a = 0.0f;
+      s_ok = exchange_collect(ex, &a) ? 1 : 0;
+      s_amax = a;
+      if (!s_ok) atomicExch(ex.status, (uint32_t)TNQ_ETIMEOUT);
+      else if (blockIdx.x == 0 && ex.amax_out) *ex.amax_out = a;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    s = scale_from_amax(s_amax, Fp8Traits<OUT>::kMax);
+  } else {
+    s = *reinterpret_cast<const volatile float*>(scale_ptr);
+    if (scale_source == TNQ_SCALE_IS_AMAX) s = scale_from_amax(s, Fp8Traits<OUT>::kMax);
+  }
+
+  const int64_t nvec = n / T::kElemsPerVec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t m = 0;
+  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+    Vec32B v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = ldg256(x + (i + u * stride) * 32);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if constexpr (AMAX) m = T::absmax(m, v[u]);
+      quant_store<IN, OUT, SAT>(v[u], s, out, i + u * stride);
+    }
+  }
+  for (; i < nvec; i += stride) {
+    const Vec32B v = ldg256(x + i * 32);
+    if constexpr (AMAX) m = T::absmax(m, v);
+    quant_store<IN, OUT, SAT>(v, s, out, i);
+  }
+  if constexpr (AMAX) m = T::fold(m);
+  if (blockIdx.x == 0) {
+    for (int64_t j = nvec * T::kElemsPerVec + threadIdx.x; j < n; j += blockDim.x) {
+      const float xv = T::load_scalar(x, j);
+      if constexpr (AMAX) m = max(m, __float_as_uint(xv) & 0x7fffffffu);
+      out[j] = (uint8_t)fp8_scalar_exact<OUT, SAT>(xv, s);
+    }
+  }
+  if constexpr (AMAX) {
+    m = block_max_u32(m, smem32);
+    uint32_t total;
+    if (grid_max(m, ws, smem32, &total)) {
+      const float amax = __uint_as_float(total);
+      ws->amax_bits = total;
+      const float old = *abs_max_inout;
+      if (!(old >= amax)) *abs_max_inout = amax;  // max(old, amax); a NaN amax wins
+    }
+  }
+}
+
+}  // namespace tnq
+
+// ================================================================= host side
+using namespace tnq;
+
+namespace tnq_host {
+thread_local int g_last_cuda_error = 0;
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+}  // namespace tnq_host
+using namespace tnq_host;
+
+// Persistent grid: as many CTAs as are resident at once (occupancy * SMs), fewer
+// for small inputs.
+template <auto Kernel>
+static int resident_ctas() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, Kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    cached[dev] = per_sm * sm_count();
+  }
+  return cached[dev];
+}
+
+template <auto Kernel>
+static int stream_grid(int64_t n_vec) {
+  int64_t want = (n_vec + kThreads - 1) / kThreads;
+  int64_t cap = resident_ctas<Kernel>();
+  if (cap > kMaxPartials) cap = kMaxPartials;
+  if (want < 1) want = 1;
+  return (int)(want < cap ? want : cap);
+}
+
+static int check_common(const void* x, int64_t n, int in_dtype, int out_dtype) {
+  if (n < 0 || (n > 0 && x == nullptr)) return TNQ_EINVAL;
+  if (in_dtype != TNQ_IN_BF16 && in_dtype != TNQ_IN_F32) return TNQ_EUNSUPPORTED;
+  if (out_dtype != TNQ_FP8_E4M3 && out_dtype != TNQ_FP8_E5M2) return TNQ_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(x) & 31u) != 0) return TNQ_EALIGN;  // 256-bit loads
+  return TNQ_OK;
+}
+
+static float fp8_max_of(int out_dtype) { return out_dtype == TNQ_FP8_E4M3 ? 448.0f : 57344.0f; }
+
+template <auto Kernel, typename... Args>
+static int launch(int64_t n_vec, cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(stream_grid<Kernel>(n_vec));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, Kernel, args...);
+  return e == cudaSuccess ? TNQ_OK : cuda_fail(e);
+}
+
+static int amax_launch(const uint8_t* xp, int64_t n, int in_dtype, Workspace* ws, float* amax_out, float* scale_out,
+                       float fmax, cudaStream_t stream) {
+  const PeerSlots none = {};
+  if (in_dtype == TNQ_IN_BF16)
+    return launch<k_amax<TNQ_IN_BF16, false>>(n / 16, stream, false, xp, n, ws, amax_out, scale_out, fmax, none);
+  return launch<k_amax<TNQ_IN_F32, false>>(n / 8, stream, false, xp, n, ws, amax_out, scale_out, fmax, none);
+}
+
+extern "C" int tnq_fp8_amax(const void* x, int64_t n, int in_dtype, int out_dtype, void* workspace,
+                            float* amax_out, tnq_stream_t stream) {
+  int rc = check_common(x, n, in_dtype, out_dtype);
+  if (rc != TNQ_OK) return rc;
+  if (workspace == nullptr) return TNQ_EINVAL;
+  Workspace* ws = static_cast<Workspace*>(workspace);
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  const float fmax = fp8_max_of(out_dtype);
+  return amax_launch(xp, n, in_dtype, ws, amax_out, nullptr, fmax, stream);
+}
+
+template <int IN, int OUT>
+static int cast_dispatch(const uint8_t* x, uint8_t* out, int64_t n, const float* scale, int scale_source,
+                         int saturated, float* abs_max, Workspace* ws, cudaStream_t stream, bool pdl,
+                         const ExchangeWait& ex) {
+  const int64_t nv = n / InTraits<IN>::kElemsPerVec;
+  if (abs_max) {
+    if (saturated) return launch<k_cast<IN, OUT, true, true>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
+    return launch<k_cast<IN, OUT, false, true>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
+  }
+  if (saturated) return launch<k_cast<IN, OUT, true, false>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
+  return launch<k_cast<IN, OUT, false, false>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
+}
+
+static int cast_any(const void* x, void* out, int64_t n, int in_dtype, int out_dtype, const float* scale,
+                    int scale_source, int saturated, float* abs_max, void* workspace, cudaStream_t stream,
+                    bool pdl, const ExchangeWait& ex = ExchangeWait{}) {
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  uint8_t* op = static_cast<uint8_t*>(out);
+  Workspace* ws = static_cast<Workspace*>(workspace);
+  if (in_dtype == TNQ_IN_BF16) {
+    if (out_dtype == TNQ_FP8_E4M3)
+      return cast_dispatch<TNQ_IN_BF16, TNQ_FP8_E4M3>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
+    return cast_dispatch<TNQ_IN_BF16, TNQ_FP8_E5M2>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
+  }
+  if (out_dtype == TNQ_FP8_E4M3)
+    return cast_dispatch<TNQ_IN_F32, TNQ_FP8_E4M3>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
+  return cast_dispatch<TNQ_IN_F32, TNQ_FP8_E5M2>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
+}
+
+extern "C" int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                                   const float* scale, int scale_source, int saturated,
+                                   float* abs_max_inout, void* workspace, tnq_stream_t stream) {
+  int rc = check_common(x, n, in_dtype, out_dtype);
+  if (rc != TNQ_OK) return rc;
+  if (scale == nullptr || (n > 0 && out == nullptr)) return TNQ_EINVAL;
+  if (scale_source != TNQ_SCALE_IS_SCALE && scale_source != TNQ_SCALE_IS_AMAX) return TNQ_EINVAL;
+  if (abs_max_inout != nullptr && workspace == nullptr) return TNQ_EINVAL;
+  if (!aligned16(out)) return TNQ_EALIGN;
+  return cast_any(x, out, n, in_dtype, out_dtype, scale, scale_source, saturated, abs_max_inout, workspace,
+                  stream, false);
+}
+
+extern "C" int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                                    void* workspace, float* scale_out, tnq_stream_t stream) {
+  int rc = check_common(x, n, in_dtype, out_dtype);
+  if (rc != TNQ_OK) return rc;
+  if (workspace == nullptr || (n > 0 && out == nullptr)) return TNQ_EINVAL;
+  if (!aligned16(out)) return TNQ_EALIGN;
+  Workspace* ws = static_cast<Workspace*>(workspace);
+  rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream);
+  if (rc != TNQ_OK) return rc;
+  return cast_any(x, out, n, in_dtype, out_dtype, &ws->scale, TNQ_SCALE_IS_SCALE, 1, nullptr, workspace, stream,
+                  true);
+}
+
+extern "C" int tnq_fp8_sharded_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                                    void* workspace, void* const* slot_buffers, int world_size, int rank,
+                                    uint32_t seq, float* amax_out, tnq_stream_t stream) {
+  int rc = check_common(x, n, in_dtype, out_dtype);
+  if (rc != TNQ_OK) return rc;
+  if (workspace == nullptr || slot_buffers == nullptr || (n > 0 && out == nullptr)) return TNQ_EINVAL;
+  if (world_size < 1 || world_size > kMaxRanks || rank < 0 || rank >= world_size || seq == 0) return TNQ_EINVAL;
+  if (!aligned16(out)) return TNQ_EALIGN;
+  PeerSlots peers = {};
+  for (int r = 0; r < world_size; ++r) {
+    if (slot_buffers[r] == nullptr) return TNQ_EINVAL;
+    peers.base[r] = static_cast<uint64_t*>(slot_buffers[r]);
+  }
+  peers.world = world_size, peers.rank = rank, peers.seq = seq;
+  Workspace* ws = static_cast<Workspace*>(workspace);
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  const float fmax = fp8_max_of(out_dtype);
+  if (in_dtype == TNQ_IN_BF16)
+    rc = launch<k_amax<TNQ_IN_BF16, true>>(n / 16, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, fmax, peers);
+  else
+    rc = launch<k_amax<TNQ_IN_F32, true>>(n / 8, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, fmax, peers);
+  if (rc != TNQ_OK) return rc;
+  ExchangeWait ex;
+  ex.slots = peers.base[rank];
+  ex.world = world_size;
+  ex.seq = seq;
+  ex.status = reinterpret_cast<uint32_t*>(peers.base[rank]) + kExchangeStatusWord;
+  ex.amax_out = amax_out;
+  return cast_any(x, out, n, in_dtype, out_dtype, &ws->scale, TNQ_SCALE_IS_SCALE, 1, nullptr, workspace, stream,
+                  true, ex);
+}
+
+extern "C" const char* tnq_status_str(int status) {
+  switch (status) {
+    case TNQ_OK: return "ok";
+    case TNQ_EINVAL: return "invalid argument";
+    case TNQ_EALIGN: return "pointer or pitch not sufficiently aligned";
+    case TNQ_ESHAPE: return "shape is not a multiple of the block size";
+    case TNQ_EUNSUPPORTED: return "unsupported dtype or size";
+    case TNQ_ECUDA: return "CUDA runtime error";
+    case TNQ_ETIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+extern "C" int tnq_last_cuda_error(void) { return tnq_host::g_last_cuda_error; }
+extern "C" int tnq_abi_version(void) { return 1; }

@@ -1,0 +1,5 @@
+from .sharded import (  # noqa: F401
+    combine_amax,
+    plan_row_shards,
+    sharded_dynamic_scaled_quant,
+)

@@ -1,0 +1,6 @@
+from .scaled_quant import (  # noqa: F401
+    dynamic_scaled_quant,
+    dynamic_scaled_quant_with_scale,
+    rowwise_scaled_quant,
+    scaled_quant,
+)
