@@ -79,6 +79,27 @@ int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int o
 int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
                          void* workspace, float* scale_out, tnq_stream_t stream);
 
+/* The same cast as tnq_fp8_dynamic_cast for callers that cannot provide (or create)
+ * device scratch: plug-ins that receive only tensors and a stream from their host
+ * framework, processes whose device memory is entirely owned by a pool reserved at
+ * start-up, loops that must never hit cudaMalloc's device-wide synchronisation.
+ * This entry point has no counterpart in the reference.
+ * It allocates nothing and frees nothing: the reduction scratch is a fixed 4 KiB
+ * array inside the library (every GPU that loads libtnq.so holds it until the
+ * process ends).  Limits, refused with TNQ_EUNSUPPORTED: n above
+ * TNQ_STATIC_MAX_ELEMENTS, and devices on which the amax launch would need more
+ * than the 1008 per-CTA slots the array has.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls on a device share the one array: the entry point re-zeroes the words
+ * that must start at zero on every call, but two calls whose kernels can overlap on
+ * the GPU (different streams without an ordering between them) race on it and give
+ * wrong results - order them, or use tnq_fp8_dynamic_cast with separate workspaces. */
+#define TNQ_STATIC_MAX_ELEMENTS (1LL << 32)
+int tnq_fp8_dynamic_cast_static(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                                float* scale_out, tnq_stream_t stream);
+int64_t tnq_fp8_dynamic_cast_static_max_elements(void);
+
 /* Row-wise dynamic cast of x[rows, cols] (row-major, contiguous).  For each
  * requested output (a null q pointer skips it) q[r, :] = sat_fp8(x[r, :] * s_r),
  * s_r = fp8_max / max(amax_r, 1e-12) written to scale[r] (fp32, [rows]).

@@ -35,6 +35,8 @@ SIGNATURES = {
     "tnq_fp8_amax": [_p, _i64, _i, _i, _p, _p, _p],
     "tnq_fp8_scaled_cast": [_p, _p, _i64, _i, _i, _p, _i, _i, _p, _p, _p],
     "tnq_fp8_dynamic_cast": [_p, _p, _i64, _i, _i, _p, _p, _p],
+    "tnq_fp8_dynamic_cast_static": [_p, _p, _i64, _i, _i, _p, _p],
+    "tnq_fp8_dynamic_cast_static_max_elements": [],
     "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p],
     "tnq_mxfp8_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "tnq_nvfp4_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p, _p],
@@ -78,6 +80,7 @@ def load():
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
                 fn.restype = _i
+            lib.tnq_fp8_dynamic_cast_static_max_elements.restype = ctypes.c_int64
             lib.tnq_status_str.argtypes = [_i]
             lib.tnq_status_str.restype = ctypes.c_char_p
             _lib = lib

@@ -428,6 +428,68 @@ extern "C" int tnq_fp8_sharded_cast(const void* x, void* out, int64_t n, int in_
                   true, ex);
 }
 
+// ================================================================= no-allocation variant
+// Dynamic per-tensor cast for callers that own no device scratch and may not create
+// any: a plug-in that is handed input and output buffers and a stream by a host
+// framework but no allocator, a serving process that gave all device memory to its
+// own pool at start-up (a later cudaMalloc fails or stalls every stream while it
+// runs), or a latency-critical loop that cannot afford cudaMalloc's implicit
+// device-wide synchronisation.  The reduction scratch that tnq_fp8_dynamic_cast takes
+// from the caller lives here in a fixed array inside the library image: every GPU
+// that loads libtnq.so carries these 4 KiB until the process exits.
+namespace tnq {
+constexpr int kStaticScratchBytes = 4096;
+constexpr int kStaticMaxCtas = (kStaticScratchBytes - 64) / 4;  // per-CTA partial maxima that fit: 1008
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+}  // namespace tnq
+
+// Device address of g_static_scratch on the current device.  In host code the name of
+// a __device__ array is only a handle for the runtime, not an address a kernel can
+// use, so the address is asked for once per device (with that device current).
+static int static_scratch_address(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return TNQ_EUNSUPPORTED;
+  void* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress((void**)&p, tnq::g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (p == nullptr) return TNQ_ECUDA;
+    __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);  // every thread would store the same value
+  }
+  *out = p;
+  return TNQ_OK;
+}
+
+extern "C" int64_t tnq_fp8_dynamic_cast_static_max_elements(void) { return TNQ_STATIC_MAX_ELEMENTS; }
+
+extern "C" int tnq_fp8_dynamic_cast_static(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
+                                           float* scale_out, tnq_stream_t stream) {
+  int rc = check_common(x, n, in_dtype, out_dtype);
+  if (rc != TNQ_OK) return rc;
+  if (n > 0 && out == nullptr) return TNQ_EINVAL;
+  if (!aligned16(out)) return TNQ_EALIGN;
+  if (n > TNQ_STATIC_MAX_ELEMENTS) return TNQ_EUNSUPPORTED;  // beyond what the fixed scratch is specified for
+  // one partial-maximum slot per CTA of the amax launch must fit in the fixed array
+  const int amax_ctas = in_dtype == TNQ_IN_BF16 ? resident_ctas<k_amax<TNQ_IN_BF16, false>>()
+                                                : resident_ctas<k_amax<TNQ_IN_F32, false>>();
+  if (amax_ctas > kStaticMaxCtas) return TNQ_EUNSUPPORTED;
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != TNQ_OK) return rc;
+  // The array keeps whatever the previous call left.  The ticket counter and the
+  // status word must start at zero (a call that was abandoned half way would
+  // otherwise poison the next one); the partial slots are overwritten before use.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 64, stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  Workspace* ws = static_cast<Workspace*>(scratch);
+  rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream);
+  if (rc != TNQ_OK) return rc;
+  return cast_any(x, out, n, in_dtype, out_dtype, &ws->scale, TNQ_SCALE_IS_SCALE, 1, nullptr, scratch, stream, true);
+}
+
 extern "C" const char* tnq_status_str(int status) {
   switch (status) {
     case TNQ_OK: return "ok";
