@@ -133,6 +133,10 @@ def cpu_baseline(name, steps, warmup, sample_rows):
     from transformer_nuggets_b200.workloads import CONFIGS, make_input
 
     cfg = CONFIGS[name]
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1
+    except Exception:
+        pass
     x = make_input(name, "cpu", rows=sample_rows)
     for _ in range(warmup):
         cpu_reference_pass(name, x)
@@ -207,6 +211,13 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.workload != HEADLINE:  # a single-GPU configuration on its own (profiler captures, sweeps)
+        if world != 1:
+            raise SystemExit("the single-GPU configurations run with --gpus 1")
+        peak, _ = measured_peak_gbs()
+        r = other_workloads(dev, peak, only=args.workload, iters=args.steps, warm=args.warmup)
+        print(json.dumps({"workload_run": args.workload, "results": r}))
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -378,9 +389,10 @@ def run_ours(args):
     print(json.dumps(line))
 
 
-def other_workloads(dev, peak):
+def other_workloads(dev, peak, only=None, iters=None, warm=None):
     """Single-GPU configurations, timed the same way (CUDA events, cold L2 by rotating
-    buffer sets larger than L2 together).  Reported beside the headline."""
+    buffer sets larger than L2 together).  Reported beside the headline.  `only`
+    restricts the run to one configuration (profiler captures)."""
     import torch
 
     import transformer_nuggets_b200 as tn
@@ -389,7 +401,12 @@ def other_workloads(dev, peak):
 
     res = {}
 
-    def timed(fn, sets, iters=30, warm=5):
+    def timed(fn, sets, n_it=30, n_warm=5):
+        n_it = iters if iters is not None else n_it
+        n_warm = warm if warm is not None else n_warm
+        return _timed(fn, sets, n_it, n_warm)
+
+    def _timed(fn, sets, iters, warm):
         for i in range(warm):
             fn(sets[i % len(sets)])
         torch.cuda.synchronize()
@@ -411,6 +428,29 @@ def other_workloads(dev, peak):
         return {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
                 "algorithmic_bytes_per_element": bpe, "note": note}
 
+    def want(name):
+        return only is None or only == name
+
+    if want("fp8_tensor"):
+        _bench_fp8_tensor(dev, res, timed, report, ws, stream)
+    if want("fp8_rowwise"):
+        _bench_rowwise(dev, res, timed, report, stream)
+    if want("mxfp8"):
+        _bench_mxfp8(dev, res, timed, report, ws, stream)
+    if want("nvfp4"):
+        _bench_nvfp4(dev, res, timed, report, ws, stream)
+    st = int(ws[_lib.WS_STATUS_WORD].item())
+    if st != 0:
+        raise SystemExit(f"device status word {st}: a bounded wait expired in a tile kernel")
+    return res
+
+
+def _bench_fp8_tensor(dev, res, timed, report, ws, stream):
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
     # per-tensor dynamic e4m3, 4096 x 4096: 8 rotating buffer sets (8 x 48 MiB > L2)
     base = make_input("fp8_tensor", dev)
     sets = [(base.clone(), torch.empty_like(base, dtype=torch.float8_e4m3fn)) for _ in range(8)]
@@ -423,6 +463,13 @@ def other_workloads(dev, peak):
     res["fp8_tensor_hot_l2"] = report("fp8_tensor", timed(f1, sets[:1], 64, 16), "hot L2: one buffer set")
     del sets
 
+
+def _bench_rowwise(dev, res, timed, report, stream):
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
     x = make_input("fp8_rowwise", dev)
     q43, q52 = torch.empty_like(x, dtype=torch.float8_e4m3fn), torch.empty_like(x, dtype=torch.float8_e5m2)
     s43 = torch.empty(x.shape[0], 1, dtype=torch.float32, device=dev)
@@ -430,10 +477,17 @@ def other_workloads(dev, peak):
 
     def f2(_):
         _lib.call("tnq_fp8_rowwise", x.data_ptr(), x.shape[0], x.shape[1], _lib.IN_BF16, q43.data_ptr(), s43.data_ptr(),
-                  q52.data_ptr(), s52.data_ptr(), stream)
+                  q52.data_ptr(), s52.data_ptr(), 0, stream)
 
     res["fp8_rowwise"] = report("fp8_rowwise", timed(f2, [None]), "input 256 MiB > L2")
     del x, q43, q52
+
+
+def _bench_mxfp8(dev, res, timed, report, ws, stream):
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
 
     x = make_input("mxfp8", dev)
     rows, cols = x.shape
@@ -456,6 +510,14 @@ def other_workloads(dev, peak):
     res["mxfp8_rowwise_only"] = report("mxfp8", timed(f3r, [None]), "row-wise output only", 2.0 + 1.0 + 1.0 / 32)
     del x, qr, qc
 
+
+def _bench_nvfp4(dev, res, timed, report, ws, stream):
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
+    status = ws.data_ptr() + 4 * _lib.WS_STATUS_WORD
     x = make_input("nvfp4", dev)
     rows, cols = x.shape
     packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev)
@@ -474,10 +536,6 @@ def other_workloads(dev, peak):
 
     res["nvfp4"] = report("nvfp4", timed(f4, [None], 20, 4), "dynamic global scale (amax pass + quantize pass)")
     res["nvfp4_given_global_amax"] = report("nvfp4", timed(f4s, [None], 20, 4), "global amax supplied", 2.5625)
-    st = int(ws[_lib.WS_STATUS_WORD].item())
-    if st != 0:
-        raise SystemExit(f"device status word {st}: a bounded wait expired in a tile kernel")
-    return res
 
 
 def main():

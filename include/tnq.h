@@ -54,6 +54,23 @@ int tnq_last_cuda_error(void);
 /* Library ABI version; bumped when a signature changes. */
 int tnq_abi_version(void);
 
+/* Process-wide tuning switches (not part of any result: outputs are identical).
+ * TNQ_OPT_CAST_REVERSE (default 1): the cast pass of the dynamic and sharded casts
+ * walks the tensor from its end, so that the tail the amax pass left in L2 is re-read
+ * from L2 instead of HBM. */
+#define TNQ_OPT_CAST_REVERSE 1
+/* TNQ_OPT_FUSED_SMALL (default 1): tnq_fp8_dynamic_cast uses the single-launch kernel
+ * that keeps the whole tensor in shared memory when it fits (up to ~33.5 MB). */
+#define TNQ_OPT_FUSED_SMALL 2
+/* TNQ_OPT_L2_KEEP_MB (default 64; 0 = off): the amax pass of the dynamic / sharded cast
+ * loads the last that-many MiB of the tensor with an L2 evict_last policy and the rest
+ * with evict_first, so more of the tail survives until the reversed cast pass.
+ * TNQ_OPT_CAST_L2_MODE (default 0): bit 0 = that cast pass loads with evict_first,
+ * bit 1 = it stores with evict_first. */
+#define TNQ_OPT_L2_KEEP_MB 3
+#define TNQ_OPT_CAST_L2_MODE 4
+int tnq_set_option(int option, int value);
+
 /* amax = max|x| over n elements, written as fp32 to ws word TNQ_WS_AMAX_WORD and,
  * if non-null, to *amax_out; ws word TNQ_WS_SCALE_WORD receives
  * fp8_max(out_dtype) / max(amax, 1e-12).
@@ -72,9 +89,10 @@ int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int o
                         const float* scale, int scale_source, int saturated,
                         float* abs_max_inout, void* workspace, tnq_stream_t stream);
 
-/* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast, as two dependent
- * launches (the second re-reads x, from L2 when x fits there).  *scale_out
- * (nullable) receives the scale.
+/* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
+ * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
+ * cooperative launch that reads x from HBM once; larger tensors take two dependent
+ * launches (the second re-reads x).  *scale_out (nullable) receives the scale.
  * Replaces `dynamic_scaled_cast` / `dynamic_scaled_quant` (fp8/scaled_quant.py:108-169). */
 int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
                          void* workspace, float* scale_out, tnq_stream_t stream);
@@ -103,10 +121,18 @@ int64_t tnq_fp8_dynamic_cast_static_max_elements(void);
 /* Row-wise dynamic cast of x[rows, cols] (row-major, contiguous).  For each
  * requested output (a null q pointer skips it) q[r, :] = sat_fp8(x[r, :] * s_r),
  * s_r = fp8_max / max(amax_r, 1e-12) written to scale[r] (fp32, [rows]).
+ * cols must be a multiple of 16 (bf16) / 8 (fp32).  `status` (nullable): device word
+ * that receives TNQ_ETIMEOUT if a bounded wait inside the kernel gives up.
  * The reference has no row-wise cast; the scale shape is the [M, 1] fp32 contract
  * of fp8/fp8_matmul.py:50-61 and the arithmetic is fp8/scaled_quant.py:132-135 per row. */
 int tnq_fp8_rowwise(const void* x, int64_t rows, int64_t cols, int in_dtype, void* q_e4m3,
-                    float* scale_e4m3, void* q_e5m2, float* scale_e5m2, tnq_stream_t stream);
+                    float* scale_e4m3, void* q_e5m2, float* scale_e5m2, uint32_t* status,
+                    tnq_stream_t stream);
+/* Tuning switches, same results either way.  set_tma: 1 = rows staged in shared memory
+ * by bulk async copies, 0 (default) = direct 256-bit global loads into registers.
+ * set_group: threads that share one row in the direct kernel (32/64/128/256), 0 = automatic. */
+int tnq_rowwise_set_tma(int on);
+int tnq_rowwise_set_group(int threads_per_row);
 
 /* MXFP8: 32-element blocks, E8M0 scale byte = exponent + 127, e4m3 payload.
  * Row-wise outputs (blocks along cols): q_row[rows, cols], sf_row for the

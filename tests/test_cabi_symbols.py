@@ -46,7 +46,7 @@ def test_bad_arguments_are_rejected_without_cuda():
     assert lib.tnq_fp8_amax(ctypes.c_void_p(64), 16, 7, 0, ctypes.c_void_p(64), None, None) == 4
     assert lib.tnq_fp8_amax(ctypes.c_void_p(72), 16, 0, 0, ctypes.c_void_p(64), None, None) == 2
     assert lib.tnq_fp8_scaled_cast(ctypes.c_void_p(64), None, 16, 0, 0, ctypes.c_void_p(64), 0, 1, None, None, None) == 1
-    assert lib.tnq_fp8_rowwise(ctypes.c_void_p(64), 4, 24, 0, ctypes.c_void_p(64), ctypes.c_void_p(64), None, None, None) == 3
+    assert lib.tnq_fp8_rowwise(ctypes.c_void_p(64), 4, 24, 0, ctypes.c_void_p(64), ctypes.c_void_p(64), None, None, None, None) == 3
     assert lib.tnq_mxfp8_quantize(ctypes.c_void_p(64), 32, 48, 0, ctypes.c_void_p(64), ctypes.c_void_p(64), None, None, 0, 0, None, None) == 3
     assert lib.tnq_mxfp8_quantize(ctypes.c_void_p(64), 32, 64, 1, ctypes.c_void_p(64), ctypes.c_void_p(64), None, None, 0, 0, None, None) == 4
     assert lib.tnq_nvfp4_quantize(ctypes.c_void_p(64), 32, 24, 0, ctypes.c_void_p(64), ctypes.c_void_p(64), ctypes.c_void_p(64), 0, None, None, None) == 3

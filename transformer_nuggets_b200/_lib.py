@@ -24,6 +24,7 @@ SCALES_RAW, SCALES_SWIZZLED = 0, 1
 SCALE_IS_SCALE, SCALE_IS_AMAX = 0, 1
 WORKSPACE_BYTES = 16384
 WS_AMAX_WORD, WS_SCALE_WORD, WS_STATUS_WORD = 1, 2, 3
+OPT_CAST_REVERSE = 1
 
 IN_DTYPES = {torch.bfloat16: IN_BF16, torch.float32: IN_F32}
 FP8_DTYPES = {torch.float8_e4m3fn: FP8_E4M3, torch.float8_e5m2: FP8_E5M2}
@@ -37,7 +38,9 @@ SIGNATURES = {
     "tnq_fp8_dynamic_cast": [_p, _p, _i64, _i, _i, _p, _p, _p],
     "tnq_fp8_dynamic_cast_static": [_p, _p, _i64, _i, _i, _p, _p],
     "tnq_fp8_dynamic_cast_static_max_elements": [],
-    "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p],
+    "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p],
+    "tnq_rowwise_set_tma": [_i],
+    "tnq_rowwise_set_group": [_i],
     "tnq_mxfp8_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "tnq_nvfp4_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p, _p],
     "tnq_pack_fp4_codes": [_p, _i64, _i64, _p, _p],
@@ -48,6 +51,7 @@ SIGNATURES = {
     "tnq_exchange_destroy": [_p],
     "tnq_exchange_status": [_p, _p],
     "tnq_fp8_sharded_cast": [_p, _p, _i64, _i, _i, _p, _p, _i, _i, ctypes.c_uint32, _p, _p],
+    "tnq_set_option": [_i, _i],
     "tnq_last_cuda_error": [],
     "tnq_abi_version": [],
 }

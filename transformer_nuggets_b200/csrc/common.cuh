@@ -8,6 +8,9 @@
 #pragma once
 
 #include <cstdint>
+#include <type_traits>
+#include <utility>
+
 #include <cuda_runtime.h>
 
 #include "../../include/tnq.h"
@@ -37,10 +40,94 @@ __device__ __forceinline__ Vec32B ldg256(const void* p) {
                : "l"(p));
   return v;
 }
+// L2 eviction-priority policies and loads / stores that carry one
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ Vec32B ldg256_hint(const void* p, uint64_t policy) {
+  Vec32B v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8], %9;"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                 "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ void stg128_hint(void* p, uint4 v, uint64_t policy) {
+  asm volatile("st.global.L1::no_allocate.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void stg64_hint(void* p, uint2 v, uint64_t policy) {
+  asm volatile("st.global.L1::no_allocate.L2::cache_hint.v2.u32 [%0], {%1,%2}, %3;" ::"l"(p), "r"(v.x), "r"(v.y),
+               "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void stg128(void* p, uint4 v) {
   asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)
                : "memory");
+}
+// 256-bit global store (sm_100)
+__device__ __forceinline__ void stg256(void* p, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t w4,
+                                       uint32_t w5, uint32_t w6, uint32_t w7) {
+  asm volatile("st.global.L1::no_allocate.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w0), "r"(w1),
+               "r"(w2), "r"(w3), "r"(w4), "r"(w5), "r"(w6), "r"(w7)
+               : "memory");
+}
+// shared-memory accesses by 32-bit shared-space address (no generic-pointer arithmetic)
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t saddr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+  return v;
+}
+// the same with a compile-time byte offset folded into the instruction
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_at(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(saddr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32_at(uint32_t saddr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(saddr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ void sts8_at(uint32_t saddr, uint32_t v) {
+  asm volatile("st.shared.u8 [%0+%1], %2;" ::"r"(saddr), "n"(OFF), "r"(v) : "memory");
+}
+// compile-time loop: f(std::integral_constant<int, 0>{}), ..., f(std::integral_constant<int, N-1>{})
+template <class F, int... Is>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, Is...>) {
+  (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(static_cast<F&&>(f), std::make_integer_sequence<int, N>{});
+}
+// named barrier ID (1..15) among COUNT threads (a multiple of 32); compile-time operands so
+// that the kernel reserves only the barriers it names
+template <int ID, int COUNT>
+__device__ __forceinline__ void named_barrier() {
+  asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory");
+}
+__device__ __forceinline__ void sts8(uint32_t saddr, uint32_t v) {
+  asm volatile("st.shared.u8 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void stg64(void* p, uint2 v) {
   asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
@@ -85,9 +172,23 @@ __device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
   }
   return r;
 }
+// four floats -> four fp8 bytes (a lowest); the two 16-bit halves are joined with a
+// register-pair move so that the second conversion can merge into the first's register
 template <int OUT>
 __device__ __forceinline__ uint32_t cvt_fp8x4(float a, float b, float c, float d) {
-  return cvt_fp8x2<OUT>(a, b) | (cvt_fp8x2<OUT>(c, d) << 16);
+  uint32_t r;
+  if constexpr (OUT == TNQ_FP8_E4M3) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r)
+        : "f"(a), "f"(b), "f"(c), "f"(d));
+  } else {
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e5m2x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e5m2x2.f32 hi, %4, %3;\n\tmov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r)
+        : "f"(a), "f"(b), "f"(c), "f"(d));
+  }
+  return r;
 }
 
 // Exact scalar cast with the corner cases of the CPU path the results are checked
@@ -145,6 +246,37 @@ template <int OUT, bool SAT>
 __device__ __forceinline__ uint32_t quant4_f32(uint4 v, float s) {
   return quant4<OUT, SAT>(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z),
                           __uint_as_float(v.w), s);
+}
+
+// Unchecked variants for callers that have established that every input and the scale
+// are finite (then no product can be NaN and saturation covers the rest).
+template <int OUT>
+__device__ __forceinline__ uint2 quant8_bf16_finite(uint4 v, float s) {
+  uint2 o;
+  o.x = cvt_fp8x4<OUT>(__fmul_rn(bf16lo(v.x), s), __fmul_rn(bf16hi(v.x), s), __fmul_rn(bf16lo(v.y), s),
+                       __fmul_rn(bf16hi(v.y), s));
+  o.y = cvt_fp8x4<OUT>(__fmul_rn(bf16lo(v.z), s), __fmul_rn(bf16hi(v.z), s), __fmul_rn(bf16lo(v.w), s),
+                       __fmul_rn(bf16hi(v.w), s));
+  return o;
+}
+template <int OUT>
+__device__ __forceinline__ uint32_t quant4_f32_finite(uint4 v, float s) {
+  return cvt_fp8x4<OUT>(__fmul_rn(__uint_as_float(v.x), s), __fmul_rn(__uint_as_float(v.y), s),
+                        __fmul_rn(__uint_as_float(v.z), s), __fmul_rn(__uint_as_float(v.w), s));
+}
+
+// bf16x2 helpers on raw 32-bit words
+__device__ __forceinline__ uint32_t max_pk_bf16(uint32_t a, uint32_t b) {  // per-half max
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// magnitude bits of a bf16 pair; the result orders like an unsigned integer per half
+__device__ __forceinline__ uint32_t mag_pk_bf16(uint32_t a) { return a & 0x7fff7fffu; }
+__device__ __forceinline__ uint32_t mul_pk_bf16(uint32_t a, uint32_t s) {  // per-half product, RNE
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(s));
+  return r;
 }
 
 // amax as fp32 -> scale = fp8_max / max(amax, 1e-12); a NaN amax stays NaN.
@@ -255,6 +387,10 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 namespace tnq_host {
 extern thread_local int g_last_cuda_error;
 int sm_count();  // SMs of the current device (cached per device)
+// single-launch path for tensors that fit in the GPU's shared memory (fp8_fused.cu)
+bool fused_plan(int64_t total_bytes, int* grid, uint32_t* slab_bytes);
+int fused_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype, void* workspace,
+                       float* scale_out, cudaStream_t stream, int grid, uint32_t slab_bytes);
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int cuda_fail(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);

@@ -105,16 +105,19 @@ struct InTraits<TNQ_IN_F32> {
 
 // 32 input bytes -> fp8 bytes, stored.
 template <int IN, int OUT, bool SAT>
-__device__ __forceinline__ void quant_store(const Vec32B& v, float s, uint8_t* out, int64_t vec_index) {
+__device__ __forceinline__ void quant_store(const Vec32B& v, float s, uint8_t* out, int64_t vec_index, bool hint,
+                                            uint64_t policy) {
   if constexpr (IN == TNQ_IN_BF16) {
     const uint2 a = quant8_bf16<OUT, SAT>(make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), s);
     const uint2 b = quant8_bf16<OUT, SAT>(make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]), s);
-    stg128(out + vec_index * 16, make_uint4(a.x, a.y, b.x, b.y));
+    if (hint) stg128_hint(out + vec_index * 16, make_uint4(a.x, a.y, b.x, b.y), policy);
+    else stg128(out + vec_index * 16, make_uint4(a.x, a.y, b.x, b.y));
   } else {
     uint2 o;
     o.x = quant4_f32<OUT, SAT>(make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), s);
     o.y = quant4_f32<OUT, SAT>(make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]), s);
-    stg64(out + vec_index * 8, o);
+    if (hint) stg64_hint(out + vec_index * 8, o, policy);
+    else stg64(out + vec_index * 8, o);
   }
 }
 
@@ -144,21 +147,38 @@ __device__ __forceinline__ bool grid_max(uint32_t cta_max_bits, Workspace* ws, u
 template <int IN, bool PUBLISH>
 __global__ void __launch_bounds__(kThreads)
     k_amax(const uint8_t* __restrict__ x, int64_t n, Workspace* ws, float* amax_out, float* scale_out, float fp8_max,
-           PeerSlots peers) {
+           PeerSlots peers, int64_t keep_from) {
   using T = InTraits<IN>;
   __shared__ uint32_t smem32[33];
   const int64_t nvec = n / T::kElemsPerVec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint32_t m = 0;
-  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
-    Vec32B v[kUnroll];
+  if (keep_from < nvec) {
+    // A cast pass over the same tensor follows and walks it from the end: ask L2 to
+    // hold on to the tail (vectors >= keep_from) and to let go of the rest first.
+    const uint64_t keep = l2_policy_evict_last(), stream = l2_policy_evict_first();
+    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+      Vec32B v[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) v[u] = ldg256(x + (i + u * stride) * 32);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t j = i + u * stride;
+        v[u] = ldg256_hint(x + j * 32, j >= keep_from ? keep : stream);
+      }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) m = T::absmax(m, v[u]);
+      for (int u = 0; u < kUnroll; ++u) m = T::absmax(m, v[u]);
+    }
+    for (; i < nvec; i += stride) m = T::absmax(m, ldg256_hint(x + i * 32, i >= keep_from ? keep : stream));
+  } else {
+    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+      Vec32B v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = ldg256(x + (i + u * stride) * 32);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) m = T::absmax(m, v[u]);
+    }
+    for (; i < nvec; i += stride) m = T::absmax(m, ldg256(x + i * 32));
   }
-  for (; i < nvec; i += stride) m = T::absmax(m, ldg256(x + i * 32));
   m = T::fold(m);
   if (blockIdx.x == 0) {  // ragged tail, fewer than one vector
     for (int64_t j = nvec * T::kElemsPerVec + threadIdx.x; j < n; j += blockDim.x)
@@ -187,7 +207,7 @@ __global__ void __launch_bounds__(kThreads)
 template <int IN, int OUT, bool SAT, bool AMAX>
 __global__ void __launch_bounds__(kThreads)
     k_cast(const uint8_t* __restrict__ x, uint8_t* __restrict__ out, int64_t n, const float* scale_ptr,
-           int scale_source, float* abs_max_inout, Workspace* ws, ExchangeWait ex) {
+           int scale_source, float* abs_max_inout, Workspace* ws, ExchangeWait ex, int reverse, int l2_mode) {
   using T = InTraits<IN>;
   __shared__ uint32_t smem32[33];
   pdl_wait();  // the scale may come from the preceding amax launch
@@ -213,21 +233,31 @@ __global__ void __launch_bounds__(kThreads)
   const int64_t nvec = n / T::kElemsPerVec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // reverse != 0 walks the tensor from its end: after an amax pass over the same tensor
+  // the most recently read (last) part is the part still in L2.
+  const int64_t first = reverse ? nvec - 1 : 0, dir = reverse ? -1 : 1;
+  // l2_mode bit 0: loads are last uses (evict first); bit 1: stores are never re-read (evict first)
+  const bool hint_ld = (l2_mode & 1) != 0, hint_st = (l2_mode & 2) != 0;
+  const uint64_t pol = l2_policy_evict_first();
   uint32_t m = 0;
   for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
     Vec32B v[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) v[u] = ldg256(x + (i + u * stride) * 32);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint8_t* src = x + (first + dir * (i + u * stride)) * 32;
+      v[u] = hint_ld ? ldg256_hint(src, pol) : ldg256(src);
+    }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if constexpr (AMAX) m = T::absmax(m, v[u]);
-      quant_store<IN, OUT, SAT>(v[u], s, out, i + u * stride);
+      quant_store<IN, OUT, SAT>(v[u], s, out, first + dir * (i + u * stride), hint_st, pol);
     }
   }
   for (; i < nvec; i += stride) {
-    const Vec32B v = ldg256(x + i * 32);
+    const int64_t j = first + dir * i;
+    const Vec32B v = hint_ld ? ldg256_hint(x + j * 32, pol) : ldg256(x + j * 32);
     if constexpr (AMAX) m = T::absmax(m, v);
-    quant_store<IN, OUT, SAT>(v, s, out, i);
+    quant_store<IN, OUT, SAT>(v, s, out, j, hint_st, pol);
   }
   if constexpr (AMAX) m = T::fold(m);
   if (blockIdx.x == 0) {
@@ -296,6 +326,31 @@ static int stream_grid(int64_t n_vec) {
   return (int)(want < cap ? want : cap);
 }
 
+static int g_cast_reverse = 1;
+static int g_fused_small = 1;
+static int g_l2_keep_mb = 64;
+static int g_cast_l2_mode = 0;
+// Walking backwards only pays once the tensor no longer fits in L2 as a whole.
+constexpr int64_t kReverseMinBytes = 96ll << 20;
+
+// First vector of the tail that the amax pass asks L2 to keep for the cast pass.
+static int64_t keep_from_vec(int64_t n, int in_dtype) {
+  const int64_t bytes = n * (in_dtype == TNQ_IN_BF16 ? 2 : 4), nvec = bytes / 32;
+  if (!g_cast_reverse || g_l2_keep_mb <= 0 || bytes <= kReverseMinBytes) return nvec;
+  const int64_t keep_vec = ((int64_t)g_l2_keep_mb << 20) / 32;
+  return keep_vec >= nvec ? 0 : nvec - keep_vec;
+}
+
+extern "C" int tnq_set_option(int option, int value) {
+  switch (option) {
+    case TNQ_OPT_CAST_REVERSE: g_cast_reverse = value ? 1 : 0; return TNQ_OK;
+    case TNQ_OPT_FUSED_SMALL: g_fused_small = value ? 1 : 0; return TNQ_OK;
+    case TNQ_OPT_L2_KEEP_MB: g_l2_keep_mb = value < 0 ? 0 : value; return TNQ_OK;
+    case TNQ_OPT_CAST_L2_MODE: g_cast_l2_mode = value & 3; return TNQ_OK;
+    default: return TNQ_EINVAL;
+  }
+}
+
 static int check_common(const void* x, int64_t n, int in_dtype, int out_dtype) {
   if (n < 0 || (n > 0 && x == nullptr)) return TNQ_EINVAL;
   if (in_dtype != TNQ_IN_BF16 && in_dtype != TNQ_IN_F32) return TNQ_EUNSUPPORTED;
@@ -323,11 +378,12 @@ static int launch(int64_t n_vec, cudaStream_t stream, bool pdl, Args... args) {
 }
 
 static int amax_launch(const uint8_t* xp, int64_t n, int in_dtype, Workspace* ws, float* amax_out, float* scale_out,
-                       float fmax, cudaStream_t stream) {
+                       float fmax, cudaStream_t stream, bool cast_follows = false) {
   const PeerSlots none = {};
+  const int64_t keep = cast_follows ? keep_from_vec(n, in_dtype) : INT64_MAX;
   if (in_dtype == TNQ_IN_BF16)
-    return launch<k_amax<TNQ_IN_BF16, false>>(n / 16, stream, false, xp, n, ws, amax_out, scale_out, fmax, none);
-  return launch<k_amax<TNQ_IN_F32, false>>(n / 8, stream, false, xp, n, ws, amax_out, scale_out, fmax, none);
+    return launch<k_amax<TNQ_IN_BF16, false>>(n / 16, stream, false, xp, n, ws, amax_out, scale_out, fmax, none, keep);
+  return launch<k_amax<TNQ_IN_F32, false>>(n / 8, stream, false, xp, n, ws, amax_out, scale_out, fmax, none, keep);
 }
 
 extern "C" int tnq_fp8_amax(const void* x, int64_t n, int in_dtype, int out_dtype, void* workspace,
@@ -344,30 +400,35 @@ extern "C" int tnq_fp8_amax(const void* x, int64_t n, int in_dtype, int out_dtyp
 template <int IN, int OUT>
 static int cast_dispatch(const uint8_t* x, uint8_t* out, int64_t n, const float* scale, int scale_source,
                          int saturated, float* abs_max, Workspace* ws, cudaStream_t stream, bool pdl,
-                         const ExchangeWait& ex) {
+                         const ExchangeWait& ex, int reverse, int l2_mode) {
   const int64_t nv = n / InTraits<IN>::kElemsPerVec;
   if (abs_max) {
-    if (saturated) return launch<k_cast<IN, OUT, true, true>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
-    return launch<k_cast<IN, OUT, false, true>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
+    if (saturated) return launch<k_cast<IN, OUT, true, true>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex, reverse, l2_mode);
+    return launch<k_cast<IN, OUT, false, true>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex, reverse, l2_mode);
   }
-  if (saturated) return launch<k_cast<IN, OUT, true, false>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
-  return launch<k_cast<IN, OUT, false, false>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex);
+  if (saturated) return launch<k_cast<IN, OUT, true, false>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex, reverse, l2_mode);
+  return launch<k_cast<IN, OUT, false, false>>(nv, stream, pdl, x, out, n, scale, scale_source, abs_max, ws, ex, reverse, l2_mode);
 }
 
 static int cast_any(const void* x, void* out, int64_t n, int in_dtype, int out_dtype, const float* scale,
                     int scale_source, int saturated, float* abs_max, void* workspace, cudaStream_t stream,
                     bool pdl, const ExchangeWait& ex = ExchangeWait{}) {
+  // a cast that follows an amax pass over the same tensor may walk it backwards
+  const int64_t in_bytes = n * (in_dtype == TNQ_IN_BF16 ? 2 : 4);
+  const bool after_amax = pdl || scale_source == TNQ_SCALE_IS_AMAX;
+  const int reverse = (after_amax && g_cast_reverse && in_bytes > kReverseMinBytes) ? 1 : 0;
+  const int l2_mode = reverse ? g_cast_l2_mode : 0;
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* op = static_cast<uint8_t*>(out);
   Workspace* ws = static_cast<Workspace*>(workspace);
   if (in_dtype == TNQ_IN_BF16) {
     if (out_dtype == TNQ_FP8_E4M3)
-      return cast_dispatch<TNQ_IN_BF16, TNQ_FP8_E4M3>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
-    return cast_dispatch<TNQ_IN_BF16, TNQ_FP8_E5M2>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
+      return cast_dispatch<TNQ_IN_BF16, TNQ_FP8_E4M3>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex, reverse, l2_mode);
+    return cast_dispatch<TNQ_IN_BF16, TNQ_FP8_E5M2>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex, reverse, l2_mode);
   }
   if (out_dtype == TNQ_FP8_E4M3)
-    return cast_dispatch<TNQ_IN_F32, TNQ_FP8_E4M3>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
-  return cast_dispatch<TNQ_IN_F32, TNQ_FP8_E5M2>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex);
+    return cast_dispatch<TNQ_IN_F32, TNQ_FP8_E4M3>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex, reverse, l2_mode);
+  return cast_dispatch<TNQ_IN_F32, TNQ_FP8_E5M2>(xp, op, n, scale, scale_source, saturated, abs_max, ws, stream, pdl, ex, reverse, l2_mode);
 }
 
 extern "C" int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
@@ -389,8 +450,14 @@ extern "C" int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_
   if (rc != TNQ_OK) return rc;
   if (workspace == nullptr || (n > 0 && out == nullptr)) return TNQ_EINVAL;
   if (!aligned16(out)) return TNQ_EALIGN;
+  if (g_fused_small) {  // the whole tensor fits in shared memory: one launch, one HBM read
+    int grid = 0;
+    uint32_t slab = 0;
+    if (fused_plan(n * (in_dtype == TNQ_IN_BF16 ? 2 : 4), &grid, &slab))
+      return fused_dynamic_cast(x, out, n, in_dtype, out_dtype, workspace, scale_out, stream, grid, slab);
+  }
   Workspace* ws = static_cast<Workspace*>(workspace);
-  rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream);
+  rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream, true);
   if (rc != TNQ_OK) return rc;
   return cast_any(x, out, n, in_dtype, out_dtype, &ws->scale, TNQ_SCALE_IS_SCALE, 1, nullptr, workspace, stream,
                   true);
@@ -414,9 +481,11 @@ extern "C" int tnq_fp8_sharded_cast(const void* x, void* out, int64_t n, int in_
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   const float fmax = fp8_max_of(out_dtype);
   if (in_dtype == TNQ_IN_BF16)
-    rc = launch<k_amax<TNQ_IN_BF16, true>>(n / 16, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, fmax, peers);
+    rc = launch<k_amax<TNQ_IN_BF16, true>>(n / 16, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, fmax, peers,
+                                           keep_from_vec(n, in_dtype));
   else
-    rc = launch<k_amax<TNQ_IN_F32, true>>(n / 8, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, fmax, peers);
+    rc = launch<k_amax<TNQ_IN_F32, true>>(n / 8, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, fmax, peers,
+                                          keep_from_vec(n, in_dtype));
   if (rc != TNQ_OK) return rc;
   ExchangeWait ex;
   ex.slots = peers.base[rank];

@@ -2,34 +2,72 @@
 // (blocks along the row) and column-wise (blocks along the column, stored
 // transposed) outputs from ONE read of the input.
 //
-// A 128x128 tile staged in shared memory by TMA is consumed twice: a row pass in
-// which four adjacent lanes own one 32-element block (conflict-free 16-byte shared
-// loads, two shuffles for the block amax, 8-byte coalesced stores), and a column
-// pass in which a thread owns two adjacent columns over 32 rows (conflict-free
-// 4-byte shared loads, 32 contiguous output bytes per column).  One tile yields
-// exactly one 512-byte atom of the swizzled 128x4 scale layout in each direction;
-// the atom is assembled in shared memory and written with 16-byte stores.
+// A 128x128 tile staged in shared memory by TMA is consumed by two groups of warps
+// at the same time.  Row pass (warps 0-7): four adjacent lanes own one 32-element
+// block - conflict-free 16-byte shared loads, two shuffles for the block amax,
+// 8-byte coalesced stores.  Column pass (warps 8-15): a thread owns two adjacent
+// columns over 32 rows - conflict-free 4-byte shared loads, one 32-byte store per
+// column.  One tile yields exactly one 512-byte atom of the swizzled 128x4 scale
+// layout per direction; it is assembled in shared memory and leaves as 16-byte stores.
 //
-// Exponent rule on the bf16 amax bits (E = biased exponent, m = 7-bit mantissa):
-//   ceil : e = E - 127 - 8 + (m > 0x60)      == ceil(log2(amax / 448))
-//   floor: e = E - 127 - 8                   == floor(log2(amax)) - 8
-// clamped to [-126, 127]; zero / subnormal amax gives -126.  x * 2^-e is exact.
+// The kernel is kept off the instruction-issue limit: |x| maxima and the power-of-two
+// scaling run on packed bf16 pairs (abs/max.bf16x2, mul.bf16x2 - exact for a power of
+// two), and only the final widening feeds cvt.rn.satfinite.e4m3x2.f32.
+//
+// Exponent rule on the bf16 amax bits m (15-bit magnitude): with
+//   ceil : E' = (m + 0x1f) >> 7     (biased exponent, +1 when the mantissa is above 1.75)
+//   floor: E' = m >> 7
+// the stored byte is max(E' - 8, 1) (= clamp(e, -126, ..) + 127) and the multiplier
+// 2^-e has the bf16 bits (254 - byte) << 7.  ceil equals ceil(log2(amax / 448)) and
+// floor equals floor(log2(amax)) - 8 for every finite bf16 amax.
+// A block that contains NaN or infinity is outside the contract (payload bytes are
+// whatever the hardware cvt gives; the scale byte comes from the exponent rule).
 #include "tile_pipeline.cuh"
+
+#ifndef TNQ_MX_MIXED_FMA
+#define TNQ_MX_MIXED_FMA 1
+#endif
 
 namespace tnq {
 
+__device__ __forceinline__ uint32_t abs_pk_bf16(uint32_t a) {
+  uint32_t r;
+  asm("abs.bf16x2 %0, %1;" : "=r"(r) : "r"(a));
+  return r;
+}
+
+// amax bits (15-bit bf16 magnitude) -> scale byte and the multiplier 2^-e as a bf16 pair
+// (same value in both halves).
 template <int MODE>
-__device__ __forceinline__ int e8m0_exponent(uint32_t amax_bf16_bits) {
-  const int E = (int)((amax_bf16_bits >> 7) & 0xffu);
-  const int m = (int)(amax_bf16_bits & 0x7fu);
-  if (E == 0) return -126;
-  int e = E - 135;
-  if (MODE == TNQ_E8M0_CEIL) e += (m > 0x60) ? 1 : 0;
-  return max(-126, min(127, e));
+__device__ __forceinline__ void e8m0_from_amax(uint32_t m16, uint32_t& byte, uint32_t& inv_pair) {
+  const int bias = (MODE == TNQ_E8M0_CEIL) ? (0x1f - 1024) : -1024;  // (m + 0x1f) >> 7, minus 8
+  byte = (uint32_t)max(((int)m16 + bias) >> 7, 1);
+  inv_pair = 0x7f007f00u - byte * 0x00800080u;  // ((254 - byte) << 7) in both halves
 }
-__device__ __forceinline__ float exp2_neg(int e) {  // 2^-e, e in [-126, 126]
-  return __uint_as_float((uint32_t)(127 - e) << 23);
+
+// two scaled bf16 pairs -> four e4m3 bytes (a.lo, a.hi, b.lo, b.hi)
+__device__ __forceinline__ uint32_t e4m3x4_from_pk(uint32_t a, uint32_t b) {
+  return cvt_fp8x4<TNQ_FP8_E4M3>(bf16lo(a), bf16hi(a), bf16lo(b), bf16hi(b));
 }
+
+// Widen-and-scale in one step: fp32 = bf16 * bf16 + (-0.0) with the mixed-precision FMA
+// of sm_100 (the product of a bf16 and a power of two is exact in fp32; adding -0.0
+// keeps the sign of a zero product).  s16 = bf16 bits of the power-of-two multiplier.
+__device__ __forceinline__ void widen_scale_pk(uint32_t w, uint16_t s16, float& lo, float& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+      "fma.rn.f32.bf16 %0, l, %3, %4;\n\tfma.rn.f32.bf16 %1, h, %3, %4;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(w), "h"(s16), "f"(-0.0f));
+}
+// two raw bf16 pairs and a power-of-two multiplier -> four e4m3 bytes
+__device__ __forceinline__ uint32_t e4m3x4_scaled(uint32_t a, uint32_t b, uint16_t s16) {
+  float a0, a1, b0, b1;
+  widen_scale_pk(a, s16, a0, a1);
+  widen_scale_pk(b, s16, b0, b1);
+  return cvt_fp8x4<TNQ_FP8_E4M3>(a0, a1, b0, b1);
+}
+
+constexpr bool g_mixed_fma = TNQ_MX_MIXED_FMA != 0;
 
 struct MxParams {
   int64_t rows, cols;
@@ -42,97 +80,216 @@ struct MxParams {
   int64_t sf_col_w;  // rows / 32
 };
 
+// Row pass by NW warps (warp index `warp` in 0..NW-1).  tile / sf_row are shared-space addresses.
+template <int MODE, int NW, bool FULL>
+__device__ __forceinline__ void mx_row_pass(const MxParams& p, uint32_t tile, uint32_t sf_row, uint32_t tr, uint32_t tc,
+                                            int warp, int lane) {
+  constexpr int R = kTileRows / NW;  // rows per warp, two per step
+  const int chunk = lane & 15;
+  const int r0 = warp * R + (lane >> 4);
+  const uint32_t src = tile + r0 * 256 + chunk * 16;
+  const int64_t grow0 = (int64_t)tr * kTileRows + r0, gcol = (int64_t)tc * kTileCols + chunk * 8;
+  uint8_t* dst = p.q_row + grow0 * p.cols + gcol;
+  const int64_t dstep = 2 * p.cols;
+  const bool col_ok = FULL || gcol < p.cols;
+  const bool sf_lane = (lane & 3) == 0;
+  const uint32_t sf_dst = sf_row + (r0 & 31) * 16 + (r0 >> 5) * 4 + (chunk >> 2);  // row r0 + 2*it: + it*32 (R <= 16)
+  static_for<R / 2>([&](auto I) {
+    constexpr int it = decltype(I)::value;
+    const uint4 v = lds128_at<it * 512>(src);
+    uint32_t m = max_pk_bf16(max_pk_bf16(abs_pk_bf16(v.x), abs_pk_bf16(v.y)),
+                             max_pk_bf16(abs_pk_bf16(v.z), abs_pk_bf16(v.w)));
+    m = max_pk_bf16(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = max_pk_bf16(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    uint32_t byte, s2;
+    e8m0_from_amax<MODE>(fold_u16x2(m), byte, s2);
+    uint2 o;
+    if (g_mixed_fma) {
+      o.x = e4m3x4_scaled(v.x, v.y, (uint16_t)s2);
+      o.y = e4m3x4_scaled(v.z, v.w, (uint16_t)s2);
+    } else {
+      o.x = e4m3x4_from_pk(mul_pk_bf16(v.x, s2), mul_pk_bf16(v.y, s2));
+      o.y = e4m3x4_from_pk(mul_pk_bf16(v.z, s2), mul_pk_bf16(v.w, s2));
+    }
+    if constexpr (FULL) {
+      stg64(dst, o);
+      if (sf_lane) sts8_at<it * 32>(sf_dst, byte);
+    } else {
+      const bool ok = col_ok && grow0 + 2 * it < p.rows;
+      if (ok) stg64(dst, o);
+      if (sf_lane) sts8_at<it * 32>(sf_dst, ok ? byte : 0u);
+    }
+    dst += dstep;
+  });
+}
+
+// Column pass by 256 threads (t in 0..255): columns 2w, 2w+1 and rows rb*32..rb*32+31.
+template <int MODE, bool FULL>
+__device__ __forceinline__ void mx_col_pass(const MxParams& p, uint32_t tile, uint32_t sf_col, uint32_t tr, uint32_t tc,
+                                            int t) {
+  const int w = t & 63, rb = t >> 6;
+  const uint32_t src = tile + rb * 32 * 256 + w * 4;
+  uint32_t v[32];
+  uint32_t m = 0;
+  static_for<32>([&](auto I) {
+    constexpr int i = decltype(I)::value;
+    v[i] = lds32_at<i * 256>(src);
+    m = max_pk_bf16(m, abs_pk_bf16(v[i]));
+  });
+  uint32_t byte_lo, byte_hi, s_lo, s_hi;
+  e8m0_from_amax<MODE>(m & 0xffffu, byte_lo, s_lo);
+  e8m0_from_amax<MODE>(m >> 16, byte_hi, s_hi);
+  const uint32_t s2 = __byte_perm(s_lo, s_hi, 0x7610);  // low half from s_lo, high half from s_hi
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = mul_pk_bf16(v[i], s2);
+  uint32_t lo[8], hi[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    lo[j] = cvt_fp8x4<TNQ_FP8_E4M3>(bf16lo(v[4 * j]), bf16lo(v[4 * j + 1]), bf16lo(v[4 * j + 2]), bf16lo(v[4 * j + 3]));
+    hi[j] = cvt_fp8x4<TNQ_FP8_E4M3>(bf16hi(v[4 * j]), bf16hi(v[4 * j + 1]), bf16hi(v[4 * j + 2]), bf16hi(v[4 * j + 3]));
+  }
+  const int64_t c = (int64_t)tc * kTileCols + 2 * w;
+  const int64_t r0 = (int64_t)tr * kTileRows + rb * 32;
+  const bool ok = FULL || (c < p.cols && r0 < p.rows);
+  if (ok) {
+    uint8_t* d0 = p.q_col + c * p.rows + r0;
+    stg256(d0, lo[0], lo[1], lo[2], lo[3], lo[4], lo[5], lo[6], lo[7]);
+    stg256(d0 + p.rows, hi[0], hi[1], hi[2], hi[3], hi[4], hi[5], hi[6], hi[7]);
+  }
+  // columns c0 = 2w, c1 = 2w + 1: (c & 31) * 16 + (c >> 5) * 4 + rb
+  const uint32_t sf0 = sf_col + ((2 * w) & 31) * 16 + (w >> 4) * 4 + rb;
+  sts8(sf0, ok ? byte_lo : 0u);
+  sts8(sf0 + 16, ok ? byte_hi : 0u);
+}
+
 template <bool ROW, bool COL, int MODE>
 struct MxOp {
   using Params = MxParams;
+  // row + column: warps 0-7 row pass, warps 8-15 column pass; row only: 16 warps on the
+  // row pass; column only: 8 warps
+  static constexpr int kThreads = ROW ? 512 : 256;
 
-  __device__ static __forceinline__ void process(const Params& p, const uint8_t* tile, uint8_t* sf, int64_t tr,
-                                                 int64_t tc) {
+  struct State {};
+  __device__ static __forceinline__ State init(const Params&) { return State{}; }
+
+  template <bool FULL>
+  __device__ static __forceinline__ void process(const Params& p, const State&, uint32_t tile, uint32_t sf, uint32_t tr,
+                                                 uint32_t tc) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if constexpr (ROW) {
-      uint8_t* sf_row = sf;  // 512 bytes
-      const int chunk = lane & 15;
-      const int64_t col0 = tc * kTileCols + chunk * 8;
-      const bool col_ok = col0 < p.cols;
-#pragma unroll 4
-      for (int it = 0; it < 8; ++it) {
-        const int r = warp * 16 + it * 2 + (lane >> 4);
-        const uint4 v = *reinterpret_cast<const uint4*>(tile + r * 256 + chunk * 16);
-        uint32_t m = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(0u, v.x), v.y), v.z), v.w);
-        m = fold_u16x2(m);
-        m = max(m, __shfl_xor_sync(0xffffffffu, m, 1));
-        m = max(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        const int e = e8m0_exponent<MODE>(m);
-        const uint2 o = quant8_bf16<TNQ_FP8_E4M3, true>(v, exp2_neg(e));
-        const int64_t row = tr * kTileRows + r;
-        const bool ok = col_ok && row < p.rows;
-        if (ok) stg64(p.q_row + row * p.cols + col0, o);
-        if ((lane & 3) == 0) sf_row[(r & 31) * 16 + (r >> 5) * 4 + (chunk >> 2)] = ok ? (uint8_t)(e + 127) : (uint8_t)0;
-      }
-    }
-    if constexpr (COL) {
-      uint8_t* sf_col = sf + 512;
-      const int w = threadIdx.x & 63, rb = threadIdx.x >> 6;
-      uint32_t vals[32];
-      uint32_t m = 0;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        vals[i] = *reinterpret_cast<const uint32_t*>(tile + (rb * 32 + i) * 256 + w * 4);
-        m = absmax_bf16x2(m, vals[i]);
-      }
-      const int e_lo = e8m0_exponent<MODE>(m & 0xffffu), e_hi = e8m0_exponent<MODE>(m >> 16);
-      const float s_lo = exp2_neg(e_lo), s_hi = exp2_neg(e_hi);
-      uint32_t lo[8], hi[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        lo[j] = quant4<TNQ_FP8_E4M3, true>(bf16lo(vals[4 * j]), bf16lo(vals[4 * j + 1]), bf16lo(vals[4 * j + 2]),
-                                           bf16lo(vals[4 * j + 3]), s_lo);
-        hi[j] = quant4<TNQ_FP8_E4M3, true>(bf16hi(vals[4 * j]), bf16hi(vals[4 * j + 1]), bf16hi(vals[4 * j + 2]),
-                                           bf16hi(vals[4 * j + 3]), s_hi);
-      }
-      const int64_t c = tc * kTileCols + 2 * w;
-      const int64_t r0 = tr * kTileRows + rb * 32;
-      const bool ok = c < p.cols && r0 < p.rows;
-      if (ok) {
-        uint8_t* d0 = p.q_col + c * p.rows + r0;
-        stg128(d0, make_uint4(lo[0], lo[1], lo[2], lo[3]));
-        stg128(d0 + 16, make_uint4(lo[4], lo[5], lo[6], lo[7]));
-        uint8_t* d1 = d0 + p.rows;
-        stg128(d1, make_uint4(hi[0], hi[1], hi[2], hi[3]));
-        stg128(d1 + 16, make_uint4(hi[4], hi[5], hi[6], hi[7]));
-      }
-      const int c0 = 2 * w, c1 = 2 * w + 1;
-      sf_col[(c0 & 31) * 16 + (c0 >> 5) * 4 + rb] = ok ? (uint8_t)(e_lo + 127) : (uint8_t)0;
-      sf_col[(c1 & 31) * 16 + (c1 >> 5) * 4 + rb] = ok ? (uint8_t)(e_hi + 127) : (uint8_t)0;
+    if constexpr (ROW && COL) {
+      if (warp < 8) mx_row_pass<MODE, 8, FULL>(p, tile, sf, tr, tc, warp, lane);
+      else mx_col_pass<MODE, FULL>(p, tile, sf + 512, tr, tc, (int)threadIdx.x - 256);
+    } else if constexpr (ROW) {
+      mx_row_pass<MODE, 16, FULL>(p, tile, sf, tr, tc, warp, lane);
+    } else {
+      mx_col_pass<MODE, FULL>(p, tile, sf + 512, tr, tc, (int)threadIdx.x);
     }
   }
 
-  // sf holds one swizzled atom per direction; write it out swizzled (whole atom) or raw.
-  __device__ static __forceinline__ void flush_one(const uint8_t* atom, uint8_t* dst, int layout, int64_t R,
-                                                   int64_t W, int64_t ar, int64_t ac) {
-    // atom covers scale rows ar*128..+127 and scale columns ac*4..+3 of an [R, W] scale matrix
+  // One swizzled atom (scale rows ar*128.., scale columns ac*4.. of an [R, W] scale matrix) from
+  // shared memory to its place: whole atom when swizzled (32 threads starting at t0), else row-major.
+  // `t0`: first of the threads that take part (32 of them for the swizzled copy, `span` for raw).
+  __device__ static __forceinline__ void flush_one(uint32_t atom, uint8_t* dst, int layout, int64_t R, int64_t W,
+                                                   int64_t ar, int64_t ac, int t0, int span) {
+    const int t = (int)threadIdx.x - t0;
     if (layout == TNQ_SCALES_SWIZZLED) {
       const int64_t ncb = (W + 3) / 4;
-      if (threadIdx.x < 32)
-        stg128(dst + (ar * ncb + ac) * 512 + threadIdx.x * 16, *reinterpret_cast<const uint4*>(atom + threadIdx.x * 16));
+      if (t >= 0 && t < 32) stg128(dst + (ar * ncb + ac) * 512 + t * 16, lds128(atom + t * 16));
     } else {
-      for (int idx = threadIdx.x; idx < 512; idx += kTileThreads) {
-        const int r = idx >> 2, c = idx & 3;
-        const int64_t gr = ar * 128 + r, gc = ac * 4 + c;
-        if (gr < R && gc < W) dst[gr * W + gc] = atom[(r & 31) * 16 + (r >> 5) * 4 + c];
+      if (t < 0 || t >= span) return;
+      for (int idx = t; idx < 128; idx += span) {  // one scale-matrix row (4 bytes) per thread
+        const int64_t gr = ar * 128 + idx;
+        if (gr >= R) continue;
+        const uint32_t four = lds32(atom + (idx & 31) * 16 + (idx >> 5) * 4);
+        for (int c = 0; c < 4; ++c)
+          if (ac * 4 + c < W) dst[gr * W + ac * 4 + c] = (uint8_t)(four >> (8 * c));
       }
     }
   }
 
-  __device__ static __forceinline__ void flush(const Params& p, const uint8_t* sf, int64_t tr, int64_t tc) {
-    if constexpr (ROW) flush_one(sf, p.sf_row, p.layout, p.rows, p.sf_row_w, tr, tc);
-    if constexpr (COL) flush_one(sf + 512, p.sf_col, p.layout, p.cols, p.sf_col_w, tc, tr);
+  __device__ static __forceinline__ void flush(const Params& p, uint32_t sf, uint32_t tr, uint32_t tc) {
+    if constexpr (ROW) flush_one(sf, p.sf_row, p.layout, p.rows, p.sf_row_w, tr, tc, 0, kThreads);
+    if constexpr (COL) flush_one(sf + 512, p.sf_col, p.layout, p.cols, p.sf_col_w, tc, tr, 0, kThreads);
   }
 };
 
+// Row + column outputs with the two passes decoupled: warps 0-7 (row pass) and warps
+// 8-15 (column pass) each walk the tile sequence at their own pace.  A group waits only
+// for the tile's data (mbarrier) and for its own members (named barrier); whichever
+// group finishes a stage second re-arms it and issues the next TMA load into it.
+template <int MODE>
+__global__ void __launch_bounds__(512, 2)
+    k_mxfp8_dual(const __grid_constant__ CUtensorMap tmap, MxParams p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
+  extern __shared__ uint8_t tnq_dyn_smem[];
+  uint8_t* const base = tile_smem_base(tnq_dyn_smem);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(base + kStages * kTileBytes);       // kStages x 8 bytes
+  uint32_t* const done = reinterpret_cast<uint32_t*>(base + kStages * kTileBytes + 32);  // kStages x 4 bytes
+  const uint32_t tile0 = smem_u32(base);
+  const uint32_t sf0 = tile0 + kStages * kTileBytes + 64;  // row atoms at +0 / +512, column atoms at +1024 / +1536
+  const uint32_t ntiles = tiles_r * tiles_c;
+  const uint32_t first = blockIdx.x;
+  const uint32_t count = first < ntiles ? (ntiles - first + gridDim.x - 1) / gridDim.x : 0;
+  const int group = threadIdx.x >> 8, gtid = threadIdx.x & 255;
+
+  TileCursor cur, ahead;
+  cur.init(first, gridDim.x, tiles_c);
+  ahead = cur;
+  auto issue = [&](uint32_t s) {  // one thread: arm stage s and load the tile at `ahead` into it
+    mbar_expect_tx(&bars[s], kTileBytes);
+    tma_load_2d(base + s * kTileBytes, &tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s]);
+  };
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars[s], 1);
+      done[s] = 0;
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  // every thread keeps `ahead` kStages tiles in front of `cur`; thread 0 also issues the first loads
+  for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+    if (threadIdx.x == 0 && s < count) issue(s);
+    ahead.advance();
+  }
+
+  uint32_t s = 0, phase = 0;
+  for (uint32_t k = 0; k < count; ++k) {
+    if (!mbar_wait(&bars[s], phase)) {
+      if (gtid == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_ETIMEOUT);
+      return;
+    }
+    const uint32_t tile = tile0 + s * kTileBytes;
+    const uint32_t sf = sf0 + (uint32_t)group * 1024u + (k & 1u) * 512u;
+    const bool full = (int64_t)(cur.tr + 1) * kTileRows <= p.rows && (int64_t)(cur.tc + 1) * kTileCols <= p.cols;
+    if (group == 0) {
+      if (full) mx_row_pass<MODE, 8, true>(p, tile, sf, cur.tr, cur.tc, gtid >> 5, gtid & 31);
+      else mx_row_pass<MODE, 8, false>(p, tile, sf, cur.tr, cur.tc, gtid >> 5, gtid & 31);
+    } else {
+      if (full) mx_col_pass<MODE, true>(p, tile, sf, cur.tr, cur.tc, gtid);
+      else mx_col_pass<MODE, false>(p, tile, sf, cur.tr, cur.tc, gtid);
+    }
+    // the group is done with the tile and its scale atom is staged
+    if (group == 0) named_barrier<1, 256>();
+    else named_barrier<2, 256>();
+    if (gtid == 0) {
+      __threadfence_block();
+      if (atomicAdd(&done[s], 1u) == 1u) {  // the other group released the stage earlier: reuse it
+        atomicExch(&done[s], 0u);
+        if (k + kStages < count) issue(s);  // `ahead` is the tile kStages after `cur`
+      }
+    }
+    if (group == 0) MxOp<true, true, MODE>::flush_one(sf, p.sf_row, p.layout, p.rows, p.sf_row_w, cur.tr, cur.tc, 0, 512);
+    else MxOp<true, true, MODE>::flush_one(sf, p.sf_col, p.layout, p.cols, p.sf_col_w, cur.tc, cur.tr, 256, 512);
+    cur.advance();
+    ahead.advance();
+    if (++s == (uint32_t)kStages) s = 0, phase ^= 1u;
+  }
+}
+
 template <bool ROW, bool COL, int MODE>
-__global__ void __launch_bounds__(kTileThreads)
-    k_mxfp8(const __grid_constant__ CUtensorMap tmap, MxParams p, int64_t tiles_r, int64_t tiles_c, uint32_t* status) {
+__global__ void __launch_bounds__((MxOp<ROW, COL, MODE>::kThreads), 2)
+    k_mxfp8(const __grid_constant__ CUtensorMap tmap, MxParams p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
   run_tile_pipeline<MxOp<ROW, COL, MODE>>(&tmap, p, tiles_r, tiles_c, status);
 }
 
@@ -143,19 +300,31 @@ using namespace tnq_host;
 
 template <bool ROW, bool COL, int MODE>
 static int launch_mx(const CUtensorMap& map, const MxParams& p, uint32_t* status, cudaStream_t stream) {
-  const int cap = tile_resident_ctas<k_mxfp8<ROW, COL, MODE>>();
+  constexpr int kThreads = MxOp<ROW, COL, MODE>::kThreads;
+  const int cap = tile_resident_ctas<k_mxfp8<ROW, COL, MODE>, kThreads>();
   if (cap < 1) return cuda_fail(cudaGetLastError());
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_mxfp8<ROW, COL, MODE><<<grid, kTileThreads, kTileSmemBytes, stream>>>(map, p, tiles_r, tiles_c, status);
+  k_mxfp8<ROW, COL, MODE><<<grid, kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
+  return check_launch();
+}
+
+template <int MODE>
+static int launch_mx_dual(const CUtensorMap& map, const MxParams& p, uint32_t* status, cudaStream_t stream) {
+  const int cap = tile_resident_ctas<k_mxfp8_dual<MODE>, 512>();
+  if (cap < 1) return cuda_fail(cudaGetLastError());
+  const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
+  const int64_t ntiles = tiles_r * tiles_c;
+  const int grid = (int)(ntiles < cap ? ntiles : cap);
+  k_mxfp8_dual<MODE><<<grid, 512, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
   return check_launch();
 }
 
 template <int MODE>
 static int launch_mx_mode(bool row, bool col, const CUtensorMap& map, const MxParams& p, uint32_t* status,
                           cudaStream_t stream) {
-  if (row && col) return launch_mx<true, true, MODE>(map, p, status, stream);
+  if (row && col) return launch_mx_dual<MODE>(map, p, status, stream);
   if (row) return launch_mx<true, false, MODE>(map, p, status, stream);
   return launch_mx<false, true, MODE>(map, p, status, stream);
 }
@@ -177,7 +346,7 @@ extern "C" int tnq_mxfp8_quantize(const void* x, int64_t rows, int64_t cols, int
   if (col && rows % 32 != 0) return TNQ_ESHAPE;
   if (rows > 0x7fffffff || cols > 0x7fffffff) return TNQ_EUNSUPPORTED;
   if (!aligned16(x) || (row && (!aligned16(q_row) || !aligned16(sf_row))) ||
-      (col && (!aligned16(q_col) || !aligned16(sf_col))))
+      (col && ((reinterpret_cast<uintptr_t>(q_col) & 31u) != 0 || !aligned16(sf_col))))
     return TNQ_EALIGN;
   CUtensorMap map;
   int rc = make_tile_map(&map, x, rows, cols);

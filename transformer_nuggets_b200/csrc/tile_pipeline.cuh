@@ -4,7 +4,7 @@
 // [rows, cols] bf16 matrix.  Tiles are brought into shared memory by 2-D TMA loads
 // (cp.async.bulk.tensor, cluster size 1, one destination CTA) into a ring of kStages
 // buffers, each guarded by an mbarrier; out-of-range parts of edge tiles arrive as
-// zeros.  One elected thread issues the loads; all 256 threads consume.  A stage is
+// zeros.  One elected thread issues the loads; all threads of the CTA consume.  A stage is
 // re-armed after the __syncthreads that ends the tile that used it, so no "empty"
 // barriers are needed.  Every wait is bounded: on expiry the CTA records
 // TNQ_ETIMEOUT in the status word and leaves.
@@ -20,74 +20,90 @@ constexpr int kTileRows = 128;
 constexpr int kTileCols = 128;
 constexpr int kTileBytes = kTileRows * kTileCols * 2;  // 32 KiB
 constexpr int kStages = 3;
-constexpr int kTileThreads = 256;
 constexpr int kSfBytes = 1024;  // per-tile scale staging (up to two 512-byte atoms)
 // ring + alignment slack + barriers + two double-buffered scale staging areas
 constexpr int kTileSmemBytes = kStages * kTileBytes + 128 + 64 + 2 * 2 * kSfBytes;
 
-struct TileShared {
-  uint8_t* tile[kStages];
-  uint64_t* full;  // [kStages]
-  uint8_t* sf[2];  // double-buffered, 2 * kSfBytes each
-};
-
-__device__ __forceinline__ TileShared carve_tile_smem(uint8_t* raw) {
-  TileShared s;
+// Shared-memory layout behind a 128-byte aligned base: kStages tiles, kStages
+// barriers (64 bytes reserved), two scale staging areas of 2 * kSfBytes each.
+__device__ __forceinline__ uint8_t* tile_smem_base(uint8_t* raw) {
   const uint32_t a = smem_u32(raw);
-  uint8_t* base = raw + ((128u - (a & 127u)) & 127u);
-#pragma unroll
-  for (int i = 0; i < kStages; ++i) s.tile[i] = base + i * kTileBytes;
-  s.full = reinterpret_cast<uint64_t*>(base + kStages * kTileBytes);
-  s.sf[0] = base + kStages * kTileBytes + 64;
-  s.sf[1] = s.sf[0] + 2 * kSfBytes;
-  return s;
+  return raw + ((128u - (a & 127u)) & 127u);
 }
 
-// Op::process(params, tile_smem, sf_smem, tile_row, tile_col)   all threads
-// Op::flush(params, sf_smem, tile_row, tile_col)                 all threads, after a __syncthreads
+// Op::kThreads                                  CTA size
+// Op::init(params) -> Op::State                  once per thread, before the first tile
+// Op::process<FULL>(params, state, tile, sf, tile_row, tile_col)
+//                                                all threads; tile / sf are 32-bit shared-space
+//                                                addresses; FULL = the tile lies inside the matrix
+// Op::flush(params, sf, tile_row, tile_col)      all threads, after a __syncthreads
+// Position of a CTA in its tile sequence (tiles blockIdx.x, + gridDim.x, ...), advanced
+// without divisions: 32-bit tile coordinates, the ring stage and its phase bit.
+struct TileCursor {
+  uint32_t tr, tc;      // tile row / column
+  uint32_t step_r, step_c, tiles_c;
+  __device__ __forceinline__ void init(uint32_t first, uint32_t stride, uint32_t tiles_c_) {
+    tiles_c = tiles_c_;
+    tr = first / tiles_c, tc = first % tiles_c;
+    step_r = stride / tiles_c, step_c = stride % tiles_c;
+  }
+  __device__ __forceinline__ void advance() {
+    tc += step_c;
+    tr += step_r;
+    if (tc >= tiles_c) tc -= tiles_c, ++tr;
+  }
+};
+
 template <class Op>
 __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const typename Op::Params& p,
-                                                  int64_t tiles_r, int64_t tiles_c, uint32_t* status) {
+                                                  uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
   extern __shared__ uint8_t tnq_dyn_smem[];
-  const TileShared sh = carve_tile_smem(tnq_dyn_smem);
-  const int64_t ntiles = tiles_r * tiles_c;
-  const int64_t first = blockIdx.x;
-  const int64_t count = first < ntiles ? (ntiles - first + gridDim.x - 1) / gridDim.x : 0;
+  uint8_t* const base = tile_smem_base(tnq_dyn_smem);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(base + kStages * kTileBytes);
+  const uint32_t tile0 = smem_u32(base);
+  const uint32_t sf0 = tile0 + kStages * kTileBytes + 64;
+  const uint32_t ntiles = tiles_r * tiles_c;
+  const uint32_t first = blockIdx.x;
+  const uint32_t count = first < ntiles ? (ntiles - first + gridDim.x - 1) / gridDim.x : 0;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(tmap);
 #pragma unroll
-    for (int s = 0; s < kStages; ++s) mbar_init(&sh.full[s], 1);
+    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
     fence_mbar_init();
   }
   __syncthreads();
+  const typename Op::State state = Op::init(p);
+  TileCursor cur, ahead;  // tile being consumed / next tile to load
+  cur.init(first, gridDim.x, tiles_c);
+  ahead = cur;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages && s < count; ++s) {
-      const int64_t t = first + (int64_t)s * gridDim.x;
-      mbar_expect_tx(&sh.full[s], kTileBytes);
-      tma_load_2d(sh.tile[s], tmap, (int32_t)((t % tiles_c) * kTileCols), (int32_t)((t / tiles_c) * kTileRows),
-                  &sh.full[s]);
+    for (uint32_t s = 0; s < (uint32_t)kStages && s < count; ++s) {
+      mbar_expect_tx(&bars[s], kTileBytes);
+      tma_load_2d(base + s * kTileBytes, tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s]);
+      ahead.advance();
     }
   }
-  for (int64_t k = 0; k < count; ++k) {
-    const int s = (int)(k % kStages);
-    const uint32_t parity = (uint32_t)((k / kStages) & 1);
-    if (!mbar_wait(&sh.full[s], parity)) {
+  uint32_t s = 0, phase = 0;
+  for (uint32_t k = 0; k < count; ++k) {
+    if (!mbar_wait(&bars[s], phase)) {
       if (threadIdx.x == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_ETIMEOUT);
       return;
     }
-    const int64_t t = first + k * gridDim.x;
-    const int64_t tr = t / tiles_c, tc = t % tiles_c;
-    uint8_t* sf = sh.sf[k & 1];
-    Op::process(p, sh.tile[s], sf, tr, tc);
+    const uint32_t sf = sf0 + (k & 1u) * (2 * kSfBytes);
+    const uint32_t tile = tile0 + s * kTileBytes;
+    const bool full = (int64_t)(cur.tr + 1) * kTileRows <= p.rows && (int64_t)(cur.tc + 1) * kTileCols <= p.cols;
+    if (full) Op::template process<true>(p, state, tile, sf, cur.tr, cur.tc);
+    else Op::template process<false>(p, state, tile, sf, cur.tr, cur.tc);
     __syncthreads();  // tile fully consumed, scale staging complete
     if (threadIdx.x == 0 && k + kStages < count) {
-      const int64_t tn = first + (k + kStages) * gridDim.x;
-      mbar_expect_tx(&sh.full[s], kTileBytes);
-      tma_load_2d(sh.tile[s], tmap, (int32_t)((tn % tiles_c) * kTileCols), (int32_t)((tn / tiles_c) * kTileRows),
-                  &sh.full[s]);
+      mbar_expect_tx(&bars[s], kTileBytes);
+      tma_load_2d(base + s * kTileBytes, tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s]);
+      ahead.advance();
     }
-    Op::flush(p, sf, tr, tc);
+    Op::flush(p, sf, cur.tr, cur.tc);
+    cur.advance();
+    if (++s == (uint32_t)kStages) s = 0, phase ^= 1u;
   }
 }
 
@@ -131,7 +147,7 @@ inline int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64
   return TNQ_OK;
 }
 
-template <auto Kernel>
+template <auto Kernel, int Threads>
 inline int tile_resident_ctas() {
   static int cached[64] = {0};
   int dev = 0;
@@ -140,7 +156,7 @@ inline int tile_resident_ctas() {
     if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tnq::kTileSmemBytes) != cudaSuccess)
       return -1;
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, Kernel, tnq::kTileThreads, tnq::kTileSmemBytes) !=
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, Kernel, Threads, tnq::kTileSmemBytes) !=
             cudaSuccess ||
         per_sm < 1)
       return -1;

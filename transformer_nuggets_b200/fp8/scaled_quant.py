@@ -130,7 +130,8 @@ def rowwise_scaled_quant(inpt_tensor: torch.Tensor, fp8_dtypes=(torch.float8_e4m
     with torch.cuda.device(dev):
         _lib.call(
             "tnq_fp8_rowwise", inpt_tensor.data_ptr(), rows, cols, _lib.IN_DTYPES[inpt_tensor.dtype],
-            _lib.ptr(q43), _lib.ptr(s43), _lib.ptr(q52), _lib.ptr(s52), _lib.stream_ptr(dev),
+            _lib.ptr(q43), _lib.ptr(s43), _lib.ptr(q52), _lib.ptr(s52),
+            _lib.workspace(dev).data_ptr() + 4 * _lib.WS_STATUS_WORD, _lib.stream_ptr(dev),
         )
     res = tuple(outs[d] for d in fp8_dtypes)
     return res[0] if len(res) == 1 else res
