@@ -334,29 +334,32 @@ def run_ours(args):
             pass
 
     # ---- end to end: pinned host buffers in, pinned host buffers out, every step ----
+    from transformer_nuggets_b200.dist.host_pipeline import HostCastPipeline
+
     host_in = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
     host_in.copy_(x)
-    host_out = torch.empty(out.shape, dtype=torch.uint8, pin_memory=True)
-    dev_in = torch.empty_like(x)
-
-    def e2e_step():
-        dev_in.copy_(host_in, non_blocking=True)
-        q, _ = sharded_dynamic_scaled_quant(dev_in, None, exchange=exchange, out=out)
-        host_out.copy_(q.view(torch.uint8), non_blocking=True)
-
-    for _ in range(min(args.warmup, 3)):
-        e2e_step()
+    host_out = [torch.empty(out.shape, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+    pipe = HostCastPipeline(x.shape, x.dtype, torch.float8_e4m3fn, dev, exchange=exchange)
+    for i in range(max(min(args.warmup, 3), 2)):
+        pipe.submit(host_in, host_out[i % 2])
+    pipe.synchronize()
     barrier()
     ev0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    pipe.s_h2d.wait_event(ev0)
+    for i in range(args.steps):
+        pipe.submit(host_in, host_out[i % 2])
+    torch.cuda.current_stream().wait_stream(pipe.s_d2h)
     ev1.record()
+    pipe.synchronize()
     barrier()
     e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+    ok_e2e = torch.equal(host_out[(args.steps - 1) % 2].view(torch.uint8), out.view(torch.uint8).cpu())
     e2e = {
         "value": cfg.algo_bytes_per_elem * total_elems / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
         "ms_per_step": e2e_ms, "h2d_bytes_per_step": x.numel() * x.element_size(), "d2h_bytes_per_step": out.numel(),
-        "api": "transformer_nuggets_b200.dist.sharded.sharded_dynamic_scaled_quant on pinned host rows",
+        "api": "transformer_nuggets_b200.dist.host_pipeline.HostCastPipeline.submit(pinned host rows -> pinned host fp8); "
+               "copies of consecutive steps overlap on separate streams",
+        "result_matches_device_path": bool(ok_e2e),
     }
     launches += 0  # the e2e and per-kernel passes are outside the timed region
 

@@ -111,3 +111,74 @@ def test_nccl_and_peer_exchange_ranks():
     results = mp.get_context("spawn").Manager().dict()
     mp.spawn(_nccl_rank, args=(world, _free_port(), results), nprocs=world, join=True)
     assert dict(results) == {r: 1 for r in range(world)}
+
+
+def test_exchange_wait_runs_out_and_reports():
+    """A peer that never publishes its amax: the cast kernel's bounded wait (about one
+    second) expires, the status word reports it and the context stays usable.  The
+    missing peer is a slot that nothing writes - no fault, no endless loop."""
+    import ctypes
+
+    local = ctypes.c_void_p()
+    handle = (ctypes.c_ubyte * 64)()
+    _lib.call("tnq_exchange_create", ctypes.byref(local), handle)
+    try:
+        ptrs = (ctypes.c_void_p * 2)(local.value, local.value)  # "rank 1" never stores anything
+        x = make_input("fp8_sharded", DEV, rows=256, cols=1024)
+        out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+        amax = torch.zeros(1, dtype=torch.float32, device=DEV)
+        ws = _lib.workspace(x.device)
+        _lib.call("tnq_fp8_sharded_cast", x.data_ptr(), out.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3,
+                  ws.data_ptr(), ptrs, 2, 0, 1, amax.data_ptr(), _lib.stream_ptr(x.device))
+        torch.cuda.synchronize()
+        status = ctypes.c_uint32(0)
+        _lib.call("tnq_exchange_status", local, ctypes.byref(status))
+        assert status.value == 6  # TNQ_ETIMEOUT
+        # the device is fine afterwards
+        q, s = tn.dynamic_scaled_quant_with_scale(x)
+        want, ws_ = oracle.fp8_dynamic_quant(x.cpu(), torch.float8_e4m3fn)
+        assert torch.equal(as_u8(q).cpu(), as_u8(want)) and torch.equal(s.cpu(), ws_)
+    finally:
+        torch.cuda.synchronize()
+        _lib.call("tnq_exchange_destroy", local)
+
+
+def test_single_rank_exchange_through_c_abi():
+    """world_size 1 through the peer-exchange entry point equals the plain dynamic cast."""
+    import ctypes
+
+    local = ctypes.c_void_p()
+    handle = (ctypes.c_ubyte * 64)()
+    _lib.call("tnq_exchange_create", ctypes.byref(local), handle)
+    try:
+        ptrs = (ctypes.c_void_p * 1)(local.value)
+        x = make_input("fp8_sharded", DEV, rows=1024, cols=2048)
+        ref = tn.dynamic_scaled_quant(x)
+        ws = _lib.workspace(x.device)
+        for seq in (1, 2, 3, 4):
+            out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+            amax = torch.zeros(1, dtype=torch.float32, device=DEV)
+            _lib.call("tnq_fp8_sharded_cast", x.data_ptr(), out.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3,
+                      ws.data_ptr(), ptrs, 1, 0, seq, amax.data_ptr(), _lib.stream_ptr(x.device))
+            torch.cuda.synchronize()
+            assert torch.equal(as_u8(out), as_u8(ref)) and amax.item() == x.abs().max().float().item()
+        status = ctypes.c_uint32(9)
+        _lib.call("tnq_exchange_status", local, ctypes.byref(status))
+        assert status.value == 0
+    finally:
+        _lib.call("tnq_exchange_destroy", local)
+
+
+def test_host_pipeline_matches_device_path():
+    from transformer_nuggets_b200.dist.host_pipeline import HostCastPipeline
+
+    x = make_input("fp8_sharded", "cpu", rows=2048, cols=1024)
+    want, _ = oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)
+    hin = x.pin_memory()
+    houts = [torch.empty(x.shape, dtype=torch.uint8).pin_memory() for _ in range(5)]
+    pipe = HostCastPipeline(x.shape, x.dtype, torch.float8_e4m3fn, torch.device(DEV, 0))
+    for h in houts:
+        pipe.submit(hin, h)
+    pipe.synchronize()
+    for h in houts:
+        assert torch.equal(h, as_u8(want))
