@@ -175,7 +175,7 @@ def run_reference(args):
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def workload_config(name, n_gpus, exchange, rows=None):
@@ -192,6 +192,28 @@ def workload_config(name, n_gpus, exchange, rows=None):
         "algorithmic_bytes_per_element": cfg.algo_bytes_per_elem,
         "l2": "inputs larger than L2 (each rank's shard is >= 256 MiB against 126 MB of L2)",
     }
+
+
+def bind_near_gpu(index):
+    """Restrict this process to the CPUs the driver reports as local to GPU `index`
+    (intersected with the CPUs it may use), so that pinned host buffers allocated
+    afterwards land on that NUMA node.  Returns a short description."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (n_cpu + 63) // 64)
+        near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        use = near & allowed
+        if not use:
+            return f"GPU-local CPUs not in this process's cpuset ({len(allowed)} CPUs allowed); unchanged"
+        os.sched_setaffinity(0, use)
+        return f"bound to {len(use)} GPU-local CPUs"
+    except Exception as e:  # NVML missing or affinity not permitted
+        return f"unchanged ({type(e).__name__})"
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -216,7 +238,7 @@ def run_ours(args):
             raise SystemExit("the single-GPU configurations run with --gpus 1")
         peak, _ = measured_peak_gbs()
         r = other_workloads(dev, peak, only=args.workload, iters=args.steps, warm=args.warmup)
-        print(json.dumps({"workload_run": args.workload, "results": r}))
+        emit({"workload_run": args.workload, "results": r})
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -279,7 +301,7 @@ def run_ours(args):
         if rank == 0:
             if sampler:
                 sampler.stop(t_load0, time.perf_counter())
-            print(json.dumps({"profile_run": True, "rows": cfg.rows, "ms_per_step": ms_step, "value": value}))
+            emit({"profile_run": True, "rows": cfg.rows, "ms_per_step": ms_step, "value": value})
         if exchange is not None:
             exchange.close()
         if world > 1:
@@ -336,9 +358,15 @@ def run_ours(args):
     # ---- end to end: pinned host buffers in, pinned host buffers out, every step ----
     from transformer_nuggets_b200.dist.host_pipeline import HostCastPipeline
 
+    ref_out, _ = sharded_dynamic_scaled_quant(x, None, exchange=exchange)  # device-resident result to compare with
+    all_cpus = os.sched_getaffinity(0)
+    numa = bind_near_gpu(local_rank)  # pinned buffers are first touched from the GPU's own NUMA node
     host_in = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
     host_in.copy_(x)
     host_out = [torch.empty(out.shape, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+    for h in host_out:
+        h.zero_()
+    os.sched_setaffinity(0, all_cpus)  # the CPU baseline leg later uses every CPU again
     pipe = HostCastPipeline(x.shape, x.dtype, torch.float8_e4m3fn, dev, exchange=exchange)
     for i in range(max(min(args.warmup, 3), 2)):
         pipe.submit(host_in, host_out[i % 2])
@@ -353,13 +381,13 @@ def run_ours(args):
     pipe.synchronize()
     barrier()
     e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
-    ok_e2e = torch.equal(host_out[(args.steps - 1) % 2].view(torch.uint8), out.view(torch.uint8).cpu())
+    ok_e2e = torch.equal(host_out[(args.steps - 1) % 2].view(torch.uint8), ref_out.view(torch.uint8).cpu())
     e2e = {
         "value": cfg.algo_bytes_per_elem * total_elems / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
         "ms_per_step": e2e_ms, "h2d_bytes_per_step": x.numel() * x.element_size(), "d2h_bytes_per_step": out.numel(),
         "api": "transformer_nuggets_b200.dist.host_pipeline.HostCastPipeline.submit(pinned host rows -> pinned host fp8); "
                "copies of consecutive steps overlap on separate streams",
-        "result_matches_device_path": bool(ok_e2e),
+        "result_matches_device_path": bool(ok_e2e), "host_numa_binding": numa,
     }
     launches += 0  # the e2e and per-kernel passes are outside the timed region
 
@@ -389,7 +417,7 @@ def run_ours(args):
         line["cpu_baseline"] = base
     if extras is not None:
         line["other_workloads"] = extras
-    print(json.dumps(line))
+    emit(line)
 
 
 def other_workloads(dev, peak, only=None, iters=None, warm=None):
@@ -541,7 +569,20 @@ def _bench_nvfp4(dev, res, timed, report, ws, stream):
     res["nvfp4_given_global_amax"] = report("nvfp4", timed(f4s, [None], 20, 4), "global amax supplied", 2.5625)
 
 
+def emit(line: dict):
+    """The one JSON line, on the real stdout (see main: fd 1 is pointed at stderr while the
+    benchmark runs so that library banners cannot land on stdout)."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
