@@ -192,8 +192,8 @@ __device__ __forceinline__ uint32_t cvt_fp8x4(float a, float b, float c, float d
 }
 
 // Exact scalar cast with the corner cases of the CPU path the results are checked
-// against: NaN keeps a sign (that of x if x is NaN, else that of a NaN scale, else
-// negative - the default NaN an x86 multiply produces for inf * 0); without
+// against: NaN keeps a sign (that of the scale if the scale is NaN, else that of a NaN x,
+// else negative - the default NaN an x86 multiply produces for inf * 0); without
 // saturation, overflow becomes NaN (e4m3fn, |y| rounds above 448, i.e. |y| > 464)
 // or infinity (e5m2, |y| >= 61440).
 template <int OUT, bool SAT>
@@ -201,8 +201,8 @@ __device__ __noinline__ uint32_t fp8_scalar_exact(float x, float scale) {
   const float y = __fmul_rn(x, scale);
   if (y != y) {
     uint32_t sign = 1u;
-    if (x != x) sign = __float_as_uint(x) >> 31;
-    else if (scale != scale) sign = __float_as_uint(scale) >> 31;
+    if (scale != scale) sign = __float_as_uint(scale) >> 31;
+    else if (x != x) sign = __float_as_uint(x) >> 31;
     return 0x7fu | (sign << 7);
   }
   uint32_t b = cvt_fp8x2<OUT>(y, 0.0f) & 0xffu;

@@ -25,21 +25,26 @@ struct FusedWorkspace {  // same memory as the per-tensor Workspace of fp8_tenso
   uint32_t status;
   uint32_t bar_count;  // pad[0]
   uint32_t bar_gen;    // pad[1]
-  uint32_t pad[10];
+  uint32_t gmax[2];    // pad[2..3]: tensor-wide maximum, one slot per barrier generation parity
+  uint32_t pad[8];
   uint32_t partial[(TNQ_WORKSPACE_BYTES - 64) / 4];
 };
 
-// All CTAs of a cooperative grid meet here.  Returns false if the others did not show
-// up within about a second.
-__device__ __forceinline__ bool grid_barrier(FusedWorkspace* ws, int* s_flag) {
-  __syncthreads();
+// All CTAs of a cooperative grid meet here and leave with the maximum of their
+// contributions.  One atomicMax into the slot of the current generation, a ticket, and
+// a generation word that the last arriver bumps (after clearing the other slot for the
+// next call).  Returns false if the others did not show up within about a second.
+__device__ __forceinline__ bool grid_max_barrier(FusedWorkspace* ws, uint32_t cta_max, uint32_t* result, int* s_flag,
+                                                 uint32_t* s_val) {
   if (threadIdx.x == 0) {
     int ok = 1;
     volatile uint32_t* gen = &ws->bar_gen;
     const uint32_t my_gen = *gen;
+    atomicMax(&ws->gmax[my_gen & 1u], cta_max);
     __threadfence();
     const uint32_t t = atomicInc(&ws->bar_count, gridDim.x - 1);  // wraps to 0 for the next use
     if (t == gridDim.x - 1) {
+      ws->gmax[(my_gen + 1u) & 1u] = 0u;
       __threadfence();
       atomicAdd(const_cast<uint32_t*>(gen), 1u);
     } else {
@@ -56,9 +61,11 @@ __device__ __forceinline__ bool grid_barrier(FusedWorkspace* ws, int* s_flag) {
       }
     }
     __threadfence();
+    *s_val = __ldcg(&ws->gmax[my_gen & 1u]);
     *s_flag = ok;
   }
   __syncthreads();
+  *result = *s_val;
   return *s_flag != 0;
 }
 
@@ -118,17 +125,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   }
   if constexpr (IN == TNQ_IN_BF16) m = fold_u16x2(m) << 16;
   m = block_max_u32(m, red);
-  if (threadIdx.x == 0) ws->partial[blockIdx.x] = m;
-
-  if (!grid_barrier(ws, flag)) {
+  uint32_t g = 0;
+  if (!grid_max_barrier(ws, m, &g, flag, reinterpret_cast<uint32_t*>(flag) + 1)) {
     if (threadIdx.x == 0) atomicExch(&ws->status, (uint32_t)TNQ_ETIMEOUT);
     return;
   }
-
-  // ---- every CTA folds all partial maxima (they sit in L2)
-  uint32_t g = 0;
-  for (uint32_t i = threadIdx.x; i < gridDim.x; i += kFusedThreads) g = max(g, __ldcg(&ws->partial[i]));
-  g = block_max_u32(g, red);
   const float amax = __uint_as_float(g);
   const float s = scale_from_amax(amax, Fp8Traits<OUT>::kMax);
   if (blockIdx.x == 0 && threadIdx.x == 0) {

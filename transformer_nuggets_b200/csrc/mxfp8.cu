@@ -59,6 +59,13 @@ __device__ __forceinline__ void widen_scale_pk(uint32_t w, uint16_t s16, float& 
       : "=f"(lo), "=f"(hi)
       : "r"(w), "h"(s16), "f"(-0.0f));
 }
+// the same with one multiplier per half (two adjacent columns with their own scales)
+__device__ __forceinline__ void widen_scale_pk2(uint32_t w, uint16_t s_lo, uint16_t s_hi, float& lo, float& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+      "fma.rn.f32.bf16 %0, l, %3, %5;\n\tfma.rn.f32.bf16 %1, h, %4, %5;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(w), "h"(s_lo), "h"(s_hi), "f"(-0.0f));
+}
 // two raw bf16 pairs and a power-of-two multiplier -> four e4m3 bytes
 __device__ __forceinline__ uint32_t e4m3x4_scaled(uint32_t a, uint32_t b, uint16_t s16) {
   float a0, a1, b0, b1;
@@ -139,14 +146,28 @@ __device__ __forceinline__ void mx_col_pass(const MxParams& p, uint32_t tile, ui
   uint32_t byte_lo, byte_hi, s_lo, s_hi;
   e8m0_from_amax<MODE>(m & 0xffffu, byte_lo, s_lo);
   e8m0_from_amax<MODE>(m >> 16, byte_hi, s_hi);
-  const uint32_t s2 = __byte_perm(s_lo, s_hi, 0x7610);  // low half from s_lo, high half from s_hi
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = mul_pk_bf16(v[i], s2);
   uint32_t lo[8], hi[8];
+  if (g_mixed_fma) {
+    const uint16_t m_lo = (uint16_t)s_lo, m_hi = (uint16_t)s_hi;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    lo[j] = cvt_fp8x4<TNQ_FP8_E4M3>(bf16lo(v[4 * j]), bf16lo(v[4 * j + 1]), bf16lo(v[4 * j + 2]), bf16lo(v[4 * j + 3]));
-    hi[j] = cvt_fp8x4<TNQ_FP8_E4M3>(bf16hi(v[4 * j]), bf16hi(v[4 * j + 1]), bf16hi(v[4 * j + 2]), bf16hi(v[4 * j + 3]));
+    for (int j = 0; j < 8; ++j) {
+      float a0, a1, a2, a3, b0, b1, b2, b3;
+      widen_scale_pk2(v[4 * j], m_lo, m_hi, a0, b0);
+      widen_scale_pk2(v[4 * j + 1], m_lo, m_hi, a1, b1);
+      widen_scale_pk2(v[4 * j + 2], m_lo, m_hi, a2, b2);
+      widen_scale_pk2(v[4 * j + 3], m_lo, m_hi, a3, b3);
+      lo[j] = cvt_fp8x4<TNQ_FP8_E4M3>(a0, a1, a2, a3);
+      hi[j] = cvt_fp8x4<TNQ_FP8_E4M3>(b0, b1, b2, b3);
+    }
+  } else {
+    const uint32_t s2 = __byte_perm(s_lo, s_hi, 0x7610);  // low half from s_lo, high half from s_hi
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = mul_pk_bf16(v[i], s2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      lo[j] = cvt_fp8x4<TNQ_FP8_E4M3>(bf16lo(v[4 * j]), bf16lo(v[4 * j + 1]), bf16lo(v[4 * j + 2]), bf16lo(v[4 * j + 3]));
+      hi[j] = cvt_fp8x4<TNQ_FP8_E4M3>(bf16hi(v[4 * j]), bf16hi(v[4 * j + 1]), bf16hi(v[4 * j + 2]), bf16hi(v[4 * j + 3]));
+    }
   }
   const int64_t c = (int64_t)tc * kTileCols + 2 * w;
   const int64_t r0 = (int64_t)tr * kTileRows + rb * 32;
