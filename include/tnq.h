@@ -202,6 +202,14 @@ int tnq_fp8_sharded_cast(const void* x, void* out, int64_t n, int in_dtype, int 
                          void* workspace, void* const* slot_buffers, int world_size, int rank,
                          uint32_t seq, float* amax_out, tnq_stream_t stream);
 
+/* Tensor-wide amax of a row-sharded tensor, for quantizers that take the amax as an
+ * input (tnq_nvfp4_quantize): local amax -> 8-byte store into every rank's slot buffer ->
+ * a one-CTA kernel waits (bounded) for all ranks' words and writes their MAX to
+ * *amax_out on this rank.  Arguments as for tnq_fp8_sharded_cast; shares its sequence
+ * numbering (every collective call of a process group uses the next number). */
+int tnq_sharded_amax(const void* x, int64_t n, int in_dtype, void* workspace, void* const* slot_buffers,
+                     int world_size, int rank, uint32_t seq, float* amax_out, tnq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

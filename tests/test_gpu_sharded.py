@@ -95,6 +95,15 @@ def _nccl_rank(rank, world, port, results):
                 torch.cuda.synchronize()
                 ok = ok and torch.equal(torch.tensor(448.0) / amax.cpu(), wscale)
                 ok = ok and torch.equal(as_u8(q).cpu(), as_u8(want[s:e]))
+            # NVFP4 with the tensor-wide scale: each rank's rows equal the same rows of the unsharded result
+            from transformer_nuggets_b200.dist.sharded import sharded_quantize_nvfp4
+
+            wp, wsf, wg = oracle.nvfp4_quantize(x)
+            got = sharded_quantize_nvfp4(x[s:e].cuda(), None, exchange=exchange, swizzle=False)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got.global_scale.cpu(), wg)
+            ok = ok and torch.equal(got.packed.view(torch.uint8).cpu(), wp[s:e])
+            ok = ok and torch.equal(as_u8(got.block_scales).cpu(), as_u8(wsf[s:e]))
             if exchange is not None:
                 ok = ok and exchange.status() == 0
                 exchange.close()
@@ -162,6 +171,11 @@ def test_single_rank_exchange_through_c_abi():
                       ws.data_ptr(), ptrs, 1, 0, seq, amax.data_ptr(), _lib.stream_ptr(x.device))
             torch.cuda.synchronize()
             assert torch.equal(as_u8(out), as_u8(ref)) and amax.item() == x.abs().max().float().item()
+        amax = torch.zeros(1, dtype=torch.float32, device=DEV)
+        _lib.call("tnq_sharded_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, ws.data_ptr(), ptrs, 1, 0, 5,
+                  amax.data_ptr(), _lib.stream_ptr(x.device))
+        torch.cuda.synchronize()
+        assert amax.item() == x.abs().max().float().item()
         status = ctypes.c_uint32(9)
         _lib.call("tnq_exchange_status", local, ctypes.byref(status))
         assert status.value == 0

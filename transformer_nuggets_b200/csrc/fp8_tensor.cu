@@ -203,6 +203,20 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// One CTA: wait (bounded) for every rank's amax word of this sequence number in this GPU's
+// own slot buffer and write their maximum.
+__global__ void k_exchange_collect(ExchangeWait ex) {
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    float a = 0.0f;
+    if (exchange_collect(ex, &a)) {
+      if (ex.amax_out) *ex.amax_out = a;
+    } else {
+      atomicExch(ex.status, (uint32_t)TNQ_ETIMEOUT);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- cast (optionally + amax)
 template <int IN, int OUT, bool SAT, bool AMAX>
 __global__ void __launch_bounds__(kThreads)
@@ -557,6 +571,46 @@ extern "C" int tnq_fp8_dynamic_cast_static(const void* x, void* out, int64_t n, 
   rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream);
   if (rc != TNQ_OK) return rc;
   return cast_any(x, out, n, in_dtype, out_dtype, &ws->scale, TNQ_SCALE_IS_SCALE, 1, nullptr, scratch, stream, true);
+}
+
+extern "C" int tnq_sharded_amax(const void* x, int64_t n, int in_dtype, void* workspace, void* const* slot_buffers,
+                                int world_size, int rank, uint32_t seq, float* amax_out, tnq_stream_t stream) {
+  int rc = check_common(x, n, in_dtype, TNQ_FP8_E4M3);
+  if (rc != TNQ_OK) return rc;
+  if (workspace == nullptr || slot_buffers == nullptr || amax_out == nullptr) return TNQ_EINVAL;
+  if (world_size < 1 || world_size > kMaxRanks || rank < 0 || rank >= world_size || seq == 0) return TNQ_EINVAL;
+  PeerSlots peers = {};
+  for (int r = 0; r < world_size; ++r) {
+    if (slot_buffers[r] == nullptr) return TNQ_EINVAL;
+    peers.base[r] = static_cast<uint64_t*>(slot_buffers[r]);
+  }
+  peers.world = world_size, peers.rank = rank, peers.seq = seq;
+  Workspace* ws = static_cast<Workspace*>(workspace);
+  const uint8_t* xp = static_cast<const uint8_t*>(x);
+  if (in_dtype == TNQ_IN_BF16)
+    rc = launch<k_amax<TNQ_IN_BF16, true>>(n / 16, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, 448.0f, peers,
+                                           (int64_t)INT64_MAX);
+  else
+    rc = launch<k_amax<TNQ_IN_F32, true>>(n / 8, stream, false, xp, n, ws, (float*)nullptr, (float*)nullptr, 448.0f, peers,
+                                          (int64_t)INT64_MAX);
+  if (rc != TNQ_OK) return rc;
+  ExchangeWait ex;
+  ex.slots = peers.base[rank];
+  ex.world = world_size;
+  ex.seq = seq;
+  ex.status = reinterpret_cast<uint32_t*>(peers.base[rank]) + kExchangeStatusWord;
+  ex.amax_out = amax_out;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, k_exchange_collect, ex);
+  return e == cudaSuccess ? TNQ_OK : cuda_fail(e);
 }
 
 extern "C" const char* tnq_status_str(int status) {

@@ -65,6 +65,23 @@ class PeerAmaxExchange:
         )
         return self._amax
 
+    def global_amax(self, local_rows: torch.Tensor) -> torch.Tensor:
+        """Enqueue: amax of this rank's rows, exchange, MAX over ranks.  Returns a new
+        one-element fp32 device tensor that will hold the tensor-wide amax."""
+        _lib.require_cuda(local_rows, "local_rows")
+        if local_rows.dtype not in _lib.IN_DTYPES or not local_rows.is_contiguous():
+            raise TypeError("local_rows must be a contiguous bfloat16 / float32 tensor")
+        dev = local_rows.device
+        out = torch.empty(1, dtype=torch.float32, device=dev)
+        self.seq = self.seq % 0xFFFFFFFF + 1
+        with torch.cuda.device(dev):
+            _lib.call(
+                "tnq_sharded_amax", local_rows.data_ptr(), local_rows.numel(), _lib.IN_DTYPES[local_rows.dtype],
+                _lib.workspace(dev).data_ptr(), self._ptrs, self.world, self.rank, self.seq, out.data_ptr(),
+                _lib.stream_ptr(dev),
+            )
+        return out
+
     def status(self) -> int:
         """0, or TNQ_ETIMEOUT if a cast kernel gave up waiting for a peer (synchronises)."""
         v = ctypes.c_uint32(0)

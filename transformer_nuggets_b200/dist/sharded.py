@@ -84,3 +84,31 @@ def sharded_dynamic_scaled_quant(
                 _lib.SCALE_IS_AMAX, 1, 0, 0, stream,
             )
     return out, amax
+
+
+def sharded_global_amax(local_rows: torch.Tensor, group=None, *, exchange=None) -> torch.Tensor:
+    """Tensor-wide ``max|x|`` of a row-sharded tensor as a one-element fp32 device tensor
+    (identical on every rank): peer-store exchange when ``exchange`` is given, else local
+    amax kernel + NCCL all-reduce(MAX)."""
+    _lib.require_cuda(local_rows, "local_rows")
+    if exchange is not None:
+        return exchange.global_amax(local_rows)
+    if local_rows.dtype not in _lib.IN_DTYPES or not local_rows.is_contiguous():
+        raise TypeError("local_rows must be a contiguous bfloat16 / float32 tensor")
+    dev = local_rows.device
+    amax = torch.empty(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("tnq_fp8_amax", local_rows.data_ptr(), local_rows.numel(), _lib.IN_DTYPES[local_rows.dtype],
+                  _lib.FP8_E4M3, _lib.workspace(dev).data_ptr(), amax.data_ptr(), _lib.stream_ptr(dev))
+    return combine_amax(amax, group)
+
+
+def sharded_quantize_nvfp4(local_rows: torch.Tensor, group=None, *, exchange=None, swizzle: bool = True):
+    """NVFP4-quantize this rank's row block of a row-sharded tensor with the global scale
+    of the WHOLE tensor.  Block scales and payload are row-local; only the tensor-wide amax
+    is exchanged.  With row blocks that are multiples of 128 rows (``plan_row_shards``) the
+    per-rank swizzled scale buffers concatenate to the unsharded one."""
+    from ..cute.nvfp4_tma import quantize_nvfp4
+
+    amax = sharded_global_amax(local_rows, group, exchange=exchange)
+    return quantize_nvfp4(local_rows, amax, swizzle=swizzle)
