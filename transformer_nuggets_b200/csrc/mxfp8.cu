@@ -366,6 +366,7 @@ extern "C" int tnq_mxfp8_quantize(const void* x, int64_t rows, int64_t cols, int
   if (row && cols % 32 != 0) return TNQ_ESHAPE;
   if (col && rows % 32 != 0) return TNQ_ESHAPE;
   if (rows > 0x7fffffff || cols > 0x7fffffff) return TNQ_EUNSUPPORTED;
+  if (((rows + 127) / 128) * ((cols + 127) / 128) > 0x7fffffff) return TNQ_EUNSUPPORTED;  // 32-bit tile cursor
   if (!aligned16(x) || (row && (!aligned16(q_row) || !aligned16(sf_row))) ||
       (col && ((reinterpret_cast<uintptr_t>(q_col) & 31u) != 0 || !aligned16(sf_col))))
     return TNQ_EALIGN;

@@ -167,6 +167,7 @@ extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int
   if (x == nullptr || packed == nullptr || sf == nullptr) return TNQ_EINVAL;
   if (cols % 16 != 0) return TNQ_ESHAPE;
   if (rows > 0x7fffffff || cols > 0x7fffffff) return TNQ_EUNSUPPORTED;
+  if (((rows + 127) / 128) * ((cols + 127) / 128) > 0x7fffffff) return TNQ_EUNSUPPORTED;  // 32-bit tile cursor
   if (!aligned16(x) || !aligned16(packed) || !aligned16(sf)) return TNQ_EALIGN;
   CUtensorMap map;
   int rc = make_tile_map(&map, x, rows, cols);
