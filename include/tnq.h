@@ -202,6 +202,26 @@ int tnq_fp8_sharded_cast(const void* x, void* out, int64_t n, int in_dtype, int 
                          void* workspace, void* const* slot_buffers, int world_size, int rank,
                          uint32_t seq, float* amax_out, tnq_stream_t stream);
 
+/* ---- block-scaled M = 1 GEMV: the consumer directly downstream of the quantizers ---- */
+
+/* y[n] = sum over 32-element blocks b of 2^(x_sf[b]-127) * 2^(w_sf[n,b]-127) *
+ * sum_{k in b} x[k] * w[n,k]; x [K] and w [N, K] e4m3, scales E8M0 bytes for the
+ * [1, K/32] and [N, K/32] scale matrices in scale_layout (RAW or SWIZZLED), fp32
+ * accumulation, y bf16 [N].  A scale byte 0xFF gives NaN.  K % 32 == 0, K <= 65536.
+ * Replaces Mxfp8TmaGemv / mxfp8_tma_gemv (cute/blockscaled_tma.py:820-1355,
+ * cute/mxfp8_tma.py:392-494). */
+int tnq_mxfp8_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, int64_t n, int64_t k,
+                   int scale_layout, void* y_bf16, tnq_stream_t stream);
+
+/* y[n] = gx * gw * sum over 16-element blocks b of x_sf[b] * w_sf[n,b] * sum_{k in b}
+ * x[k] * w[n,k]; x [K/2] and w [N, K/2] packed e2m1 (low nibble first), block scales
+ * e4m3 bytes, *x_global / *w_global optional fp32 tensorwise scales (null = 1).
+ * K % 32 == 0, K <= 65536.  Replaces Nvfp4TmaGemv / nvfp4_tma_gemv
+ * (cute/nvfp4_tma.py:833-938, decode convention cute/blockscaled_tma.py:807-818). */
+int tnq_nvfp4_gemv(const void* x_packed, const void* w_packed, const void* x_sf, const void* w_sf,
+                   const float* x_global, const float* w_global, int64_t n, int64_t k, int scale_layout,
+                   void* y_bf16, tnq_stream_t stream);
+
 /* Tensor-wide amax of a row-sharded tensor, for quantizers that take the amax as an
  * input (tnq_nvfp4_quantize): local amax -> 8-byte store into every rank's slot buffer ->
  * a one-CTA kernel waits (bounded) for all ranks' words and writes their MAX to

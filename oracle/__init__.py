@@ -25,6 +25,9 @@ from .cast_oracle import (  # noqa: F401
     fp8_dynamic_quant,
     fp8_rowwise_quant,
     fp8_scaled_quant,
+    mxfp8_dequantize,
+    mxfp8_gemv,
+    nvfp4_gemv,
     mxfp8_quantize,
     nvfp4_dequantize,
     nvfp4_quantize,

@@ -301,3 +301,33 @@ def nvfp4_dequantize(packed: torch.Tensor, s_q: torch.Tensor, g_dec: torch.Tenso
     codes = torch.stack([lo, hi], dim=-1).reshape(packed.shape[0], -1)
     vals = e2m1_decode(codes).reshape(packed.shape[0], -1, 16)
     return (vals * s_q.to(torch.float32).unsqueeze(-1) * g_dec).reshape(packed.shape[0], -1)
+
+
+# --------------------------------------------------------------------------- #
+# block-scaled M = 1 GEMV (the consumer of the quantizers' outputs)            #
+# --------------------------------------------------------------------------- #
+def mxfp8_dequantize(q: torch.Tensor, scale_u8: torch.Tensor) -> torch.Tensor:
+    """e4m3 payload * 2^(byte-127) per 32-element block -> fp32.  Follows
+    ``dequantize_mxfp8`` of the reference's tests (test/test_mxfp8_tma.py:89-93) and the
+    byte semantics of ``combined_e8m0_to_f32`` (cute/mxfp8_tma.py:28-42): 0xFF is NaN."""
+    s = torch.exp2(scale_u8.to(torch.float64) - 127.0).to(torch.float32)
+    s = torch.where(scale_u8 == 255, torch.full_like(s, float("nan")), s)
+    return q.to(torch.float32) * s.repeat_interleave(32, dim=1)
+
+
+def mxfp8_gemv(q_input, weight, input_scale, weight_scale) -> torch.Tensor:
+    """[1, K] x [N, K]^T with raw E8M0 scales -> [1, N] bf16: the dequantised fp32 matmul
+    the reference checks its GEMV against (test/test_mxfp8_tma.py:113-140, atol 1.0,
+    rtol 0.05).  Floating point: compared with a tolerance, not bit for bit."""
+    return (mxfp8_dequantize(q_input, input_scale) @ mxfp8_dequantize(weight, weight_scale).T).to(torch.bfloat16)
+
+
+def nvfp4_gemv(q_input_packed, weight_packed, input_scale, weight_scale, input_global=None, weight_global=None):
+    """Packed e2m1 [1, K/2] x [N, K/2]^T with raw e4m3 block scales and optional fp32
+    tensorwise scales -> [1, N] bf16 (test/test_nvfp4_tma.py:186-224, 376-397: decode,
+    accumulate, then multiply by the global scales; atol 2.0, rtol 0.05)."""
+    one = torch.ones(1)
+    a = nvfp4_dequantize(q_input_packed, input_scale, one)
+    b = nvfp4_dequantize(weight_packed, weight_scale, one)
+    g = (one if input_global is None else input_global.float().cpu()) * (one if weight_global is None else weight_global.float().cpu())
+    return ((a @ b.T) * g).to(torch.bfloat16)

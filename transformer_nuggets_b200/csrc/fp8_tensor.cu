@@ -2,16 +2,23 @@
 // side output) and the dynamic cast (amax -> scale -> saturated cast).
 //
 // All three are HBM streaming kernels.  Persistent grids (a multiple of the SM
-// count), grid-stride over 32-byte vectors, four independent 256-bit loads in
-// flight per thread, |x| maxima on the integer view, one warp `redux` + one shared
+// count), grid-stride over 32-byte vectors, 512-thread CTAs with two independent
+// 256-bit loads in flight per thread (the best of a sweep over 128..1024 threads and
+// unroll 1..8; 640- and 768-thread CTAs lose 7-12 %), |x| maxima on the integer view, one warp `redux` + one shared
 // memory step per CTA, and a self-resetting ticket so that the last CTA to finish
 // combines the per-CTA partial maxima (no float atomics, no memset between calls).
 #include "common.cuh"
 
 namespace tnq {
 
-constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
+#ifndef TNQ_STREAM_THREADS
+#define TNQ_STREAM_THREADS 512
+#endif
+#ifndef TNQ_STREAM_UNROLL
+#define TNQ_STREAM_UNROLL 2
+#endif
+constexpr int kThreads = TNQ_STREAM_THREADS;
+constexpr int kUnroll = TNQ_STREAM_UNROLL;
 constexpr int kMaxPartials = (TNQ_WORKSPACE_BYTES - 64) / 4;
 
 struct Workspace {
@@ -145,7 +152,7 @@ __device__ __forceinline__ bool grid_max(uint32_t cta_max_bits, Workspace* ws, u
 
 // ---------------------------------------------------------------- amax
 template <int IN, bool PUBLISH>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads)
     k_amax(const uint8_t* __restrict__ x, int64_t n, Workspace* ws, float* amax_out, float* scale_out, float fp8_max,
            PeerSlots peers, int64_t keep_from) {
   using T = InTraits<IN>;

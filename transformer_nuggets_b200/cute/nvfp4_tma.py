@@ -86,3 +86,101 @@ def quantize_nvfp4(x: torch.Tensor, global_amax: torch.Tensor | None = None, *, 
                 ws.data_ptr() + 4 * _lib.WS_STATUS_WORD, stream,
             )
     return NVFP4Result(packed.view(torch.float4_e2m1fn_x2), sf, gscale)
+
+
+# --------------------------------------------------------------------------- consumer
+from .blockscaled_tma import BlockScaleLayout, GridScheduler  # noqa: E402,F401
+
+
+def _check_global_scale(name, t, device):
+    if t is None:
+        return
+    if not isinstance(t, torch.Tensor) or t.dtype != torch.float32 or t.numel() != 1 or t.device != device:
+        raise ValueError(f"{name} must be a one-element float32 tensor on the input device")
+
+
+def nvfp4_tma_gemv(
+    q_input: torch.Tensor,
+    weight: torch.Tensor,
+    input_scale: torch.Tensor,
+    weight_scale: torch.Tensor,
+    *,
+    block_n: int | None = None,
+    num_stages: int = 2,
+    input_global_scale: torch.Tensor | None = None,
+    weight_global_scale: torch.Tensor | None = None,
+    output: torch.Tensor | None = None,
+    num_compute_warps: int | None = None,
+    grid_scheduler: GridScheduler = GridScheduler.STATIC,
+    num_persistent_ctas: int | None = None,
+    block_scale_layout: BlockScaleLayout = BlockScaleLayout.SWIZZLE_32_4_4,
+) -> torch.Tensor:
+    """Compute M=1 NVFP4 GEMV: packed FP4 input ``[1, K/2]`` and weight ``[N, K/2]``
+    (``float4_e2m1fn_x2`` or uint8), E4M3 block scales (canonically swizzled as in the
+    reference, or raw with ``block_scale_layout=RAW``), optional tensorwise fp32 scales
+    multiplied in at the end -> ``[1, N]`` bf16.  Contract of cute/nvfp4_tma.py:833-938;
+    the reference's tuning arguments are accepted and not needed."""
+    if q_input.ndim != 2 or weight.ndim != 2:
+        raise ValueError("q_input and weight must be rank-2 tensors")
+    for name, t in (("q_input", q_input), ("weight", weight), ("input_scale", input_scale), ("weight_scale", weight_scale)):
+        if not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous CUDA tensor")
+    for name, t in (("q_input", q_input), ("weight", weight)):
+        if t.dtype not in (torch.float4_e2m1fn_x2, torch.uint8):
+            raise TypeError(f"{name} must use torch.float4_e2m1fn_x2 (or uint8) packed storage")
+    layout = BlockScaleLayout(block_scale_layout)
+    k = q_input.shape[1] * 2
+    n = weight.shape[0]
+    if q_input.shape[0] != 1 or weight.shape[1] * 2 != k:
+        raise ValueError("q_input must be [1, K/2] and weight [N, K/2] packed bytes")
+    if k % 32 != 0 or k == 0:
+        raise ValueError("K must be a positive multiple of 32")
+    sf_k = k // 16
+    if input_scale.element_size() != 1 or weight_scale.element_size() != 1:
+        raise TypeError("block scales must use one-byte E4M3 storage")
+    if layout is BlockScaleLayout.RAW:
+        want = (sf_k, n * sf_k)
+    else:
+        padded = ((sf_k + 3) // 4) * 4
+        want = (128 * padded, ((n + 127) // 128) * 128 * padded)
+    if input_scale.numel() != want[0] or weight_scale.numel() != want[1]:
+        raise ValueError(f"block scales must contain {want[0]} (input) and {want[1]} (weight) elements")
+    dev = q_input.device
+    _check_global_scale("input_global_scale", input_global_scale, dev)
+    _check_global_scale("weight_global_scale", weight_global_scale, dev)
+    if output is None:
+        output = torch.empty((1, n), dtype=torch.bfloat16, device=dev)
+    elif (tuple(output.shape) != (1, n) or output.dtype != torch.bfloat16 or output.device != dev
+          or not output.is_contiguous()):
+        raise ValueError("output must be a contiguous [1, N] BF16 tensor on the input device")
+    with torch.cuda.device(dev):
+        _lib.call(
+            "tnq_nvfp4_gemv", q_input.data_ptr(), weight.data_ptr(), input_scale.data_ptr(), weight_scale.data_ptr(),
+            _lib.ptr(input_global_scale), _lib.ptr(weight_global_scale), n, k,
+            _lib.SCALES_RAW if layout is BlockScaleLayout.RAW else _lib.SCALES_SWIZZLED, output.data_ptr(),
+            _lib.stream_ptr(dev),
+        )
+    return output
+
+
+def nvfp4_tma_scaled_mm(
+    mat_a: torch.Tensor,
+    mat_b: torch.Tensor,
+    scale_a: torch.Tensor,
+    scale_b: torch.Tensor,
+    *,
+    block_n: int | None = None,
+    global_scale_a: torch.Tensor | None = None,
+    global_scale_b: torch.Tensor | None = None,
+    output: torch.Tensor | None = None,
+    **tuning,
+) -> torch.Tensor:
+    """M=1 subset with scaled_mm's blocked-scale and transposed-B convention: ``mat_b`` is
+    the metadata transpose of contiguous ``[N, K/2]`` packed storage."""
+    if mat_b.ndim != 2:
+        raise ValueError("mat_b must be rank-2")
+    weight = mat_b.t()
+    if not weight.is_contiguous():
+        raise ValueError("mat_b must be a metadata transpose of contiguous [N, K] storage")
+    return nvfp4_tma_gemv(mat_a, weight, scale_a, scale_b, block_n=block_n, input_global_scale=global_scale_a,
+                          weight_global_scale=global_scale_b, output=output)
