@@ -466,17 +466,18 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_mxfp8(dev, res, timed, report, ws, stream)
     if want("nvfp4"):
         _bench_nvfp4(dev, res, timed, report, ws, stream)
-    if want("gemv"):
-        _bench_gemv(dev, res, timed, peak, stream)
+    if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
+        _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
     st = int(ws[_lib.WS_STATUS_WORD].item())
     if st != 0:
         raise SystemExit(f"device status word {st}: a bounded wait expired in a tile kernel")
     return res
 
 
-def _bench_gemv(dev, res, timed, peak, stream):
+def _bench_gemv(dev, res, timed, peak, stream, which=None):
     """Block-scaled M = 1 GEMV on weights larger than L2 (the consumer of the quantizers'
-    outputs).  Algorithmic bytes: the weight payload and block scales once, x, y."""
+    outputs).  Algorithmic bytes: the weight payload and block scales once, x, y.
+    ``which`` restricts the run to "gemv_mxfp8" or "gemv_nvfp4" (one kernel per profile)."""
     import torch
 
     import transformer_nuggets_b200 as tn
@@ -489,20 +490,24 @@ def _bench_gemv(dev, res, timed, peak, stream):
         return {"us": us, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
                 "algorithmic_bytes": nbytes, "note": note}
 
-    n, k = 32768, 8192
-    w = torch.randn(n, k, dtype=torch.bfloat16, device=dev, generator=g)
-    x = torch.randn(1, k, dtype=torch.bfloat16, device=dev, generator=g)
-    rw, rx = tn.quantize_mxfp8(w, swizzle=True), tn.quantize_mxfp8(x, swizzle=True)
-    del w
-    y = torch.empty(1, n, dtype=torch.bfloat16, device=dev)
+    if which in (None, "gemv_mxfp8"):
+        n, k = 32768, 8192
+        w = torch.randn(n, k, dtype=torch.bfloat16, device=dev, generator=g)
+        x = torch.randn(1, k, dtype=torch.bfloat16, device=dev, generator=g)
+        rw, rx = tn.quantize_mxfp8(w, swizzle=True), tn.quantize_mxfp8(x, swizzle=True)
+        del w
+        y = torch.empty(1, n, dtype=torch.bfloat16, device=dev)
 
-    def f8(_):
-        _lib.call("tnq_mxfp8_gemv", rx.q_row.data_ptr(), rw.q_row.data_ptr(), rx.scale_row.data_ptr(),
-                  rw.scale_row.data_ptr(), n, k, _lib.SCALES_SWIZZLED, y.data_ptr(), stream)
+        def f8(_):
+            _lib.call("tnq_mxfp8_gemv", rx.q_row.data_ptr(), rw.q_row.data_ptr(), rx.scale_row.data_ptr(),
+                      rw.scale_row.data_ptr(), n, k, _lib.SCALES_SWIZZLED, y.data_ptr(), stream)
 
-    nbytes = n * k * (1 + 1 / 32) + k * (1 + 1 / 32) + 2 * n
-    res["gemv_mxfp8"] = report(timed(f8, [None]) * 1e3, nbytes, f"N={n} K={k}, swizzled E8M0 scales, weights 256 MiB > L2")
-    del rw
+        nbytes = n * k * (1 + 1 / 32) + k * (1 + 1 / 32) + 2 * n
+        res["gemv_mxfp8"] = report(timed(f8, [None]) * 1e3, nbytes,
+                                   f"N={n} K={k}, swizzled E8M0 scales, weights 256 MiB > L2")
+        del rw
+    if which not in (None, "gemv_nvfp4"):
+        return
 
     n, k = 32768, 16384
     w = torch.randn(n, k, dtype=torch.bfloat16, device=dev, generator=g)

@@ -6,21 +6,23 @@
 // swizzled 128x4 storage, fp32 accumulation, bf16 output.
 //
 // The weight matrix is read once from HBM; x is decoded once per CTA into shared memory as
-// fp16 together with its block factors.  A team of T warps owns four output rows at a time
-// - rows i, i + 32, i + 64, i + 96 of a 128-row tile, whose swizzled scale bytes for four
-// consecutive block columns are 16 contiguous bytes, so one 16-byte load per lane and step
-// brings every scale the lane needs - and walks K together: in one step lane j of the team
-// fetches the j-th 16-byte chunk of each row.  The next step's loads are issued into a
-// second register buffer before the current one is consumed.
+// fp16 together with its block factors.  A warp owns four output rows at a time - rows i,
+// i + 32, i + 64, i + 96 of a 128-row tile, whose swizzled scale bytes for four consecutive
+// block columns are 16 contiguous bytes, so one 16-byte copy per lane and step brings every
+// scale the lane needs - and walks K in 512-byte steps: lane j takes the j-th 16-byte chunk
+// of each row.  The chunks travel through lane-private cp.async rings in shared memory (see
+// the kernel), several steps ahead of their use.
 //
 // The inner loop is sized by instruction issue, not by arithmetic: payload bytes feed the
-// hardware converters straight from the loaded words (cvt.rn.f16x2.e2m1x2 / e4m3x2 take a
-// byte / half of a register without an extract), scale bytes go through cvt as well
-// (ue8m0x2 -> bf16x2, e4m3x2 -> f16x2), MXFP8 accumulates exact products in fp32 with the
-// mixed-precision FMA (fma.rn.f32.f16), NVFP4 sums the eight products of a half block
+// hardware converters straight from the fetched words (cvt.rn.f16x2.e2m1x2 / e4m3x2 take a
+// byte / half of a 32-bit register without an extract; the source must be a full 32-bit
+// word, which is why x is decoded from 32-bit loads too), scale bytes go through cvt as
+// well (ue8m0x2 -> bf16x2, e4m3x2 -> f16x2), MXFP8 accumulates exact products in fp32 with
+// the mixed-precision FMA (fma.rn.f32.f16), NVFP4 sums the eight products of a half block
 // exactly in fp16x2 (|sum| <= 288) before widening, and all per-row address arithmetic is
-// one 32 x 32 -> 64-bit multiply-add per load.  Lanes are folded with shuffles and the
-// team's warps through shared memory in a fixed order, so results do not depend on the grid.
+// one 32 x 32 -> 64-bit multiply-add per copy.  Lanes are folded with shuffles at the end
+// of a row group; every output row is produced by one warp in a fixed order, so results do
+// not depend on the grid.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -36,7 +38,11 @@ namespace tnq {
 #endif
 constexpr int kGemvThreads = TNQ_GEMV_THREADS;
 constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kGemvRows = 4;  // rows per team and step
+constexpr int kGemvRows = 4;  // rows per warp and step
+#ifndef TNQ_GEMV_STAGES
+#define TNQ_GEMV_STAGES 4
+#endif
+constexpr int kGemvStages = TNQ_GEMV_STAGES;  // slots per lane ring: kGemvStages - 1 steps of copies in flight
 
 // 2^(byte - 127) as fp32; byte 0 -> 2^-127 (subnormal), byte 255 -> NaN
 __device__ __forceinline__ float e8m0_to_f32(uint32_t byte) {
@@ -137,29 +143,40 @@ __host__ __device__ constexpr int gemv_x_bytes(int k) {
   return ((chunks + 31) / 32) * 32 * (FP4 ? 64 : 32);
 }
 
-// One step of one lane: a 16-byte weight chunk of each row and the rows' scale bytes
-// (component r of `sv`: row r's scale byte(s) for this chunk at bit `sh`).
-struct GemvLoads {
-  uint4 w[kGemvRows];
-  uint4 sv;
-};
+// ---------------------------------------------------------------- the kernel
+// One warp owns one row group at a time.  Every lane keeps a private ring of kGemvStages
+// slots in shared memory; a slot holds the lane's 16-byte chunk of each of the four rows and
+// (swizzled layout) the 16-byte piece with the rows' scale bytes.  Slots are filled with
+// cp.async (one commit group per step) kGemvStages - 1 steps ahead of consumption, so the
+// bytes in flight are bounded by shared memory rather than by registers or by the order in
+// which register loads retire, and no lane ever reads a slot another lane wrote: the
+// pipeline needs neither a barrier nor a warp synchronisation.
+constexpr int kSlotBytes = (kGemvRows + 1) * 512;  // per warp: 4 rows x 512 B + 512 B of scale pieces
 
-template <bool FP4, int T>
+__device__ __forceinline__ void cp_async16(uint32_t saddr, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <bool FP4>
 __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
     k_blockscaled_gemv(const uint8_t* __restrict__ w, const uint8_t* __restrict__ x, const uint8_t* __restrict__ x_sf,
                        const uint8_t* __restrict__ w_sf, const float* __restrict__ x_global,
                        const float* __restrict__ w_global, uint32_t n, uint32_t k, int layout,
                        uint16_t* __restrict__ y) {
   using F = GemvFmt<FP4>;
-  constexpr int kTeams = kGemvWarps / T;
   constexpr int Q = FP4 ? 4 : 2;  // 16-byte pieces of fp16 x per 16-byte weight chunk
+  constexpr int S = kGemvStages;
   extern __shared__ __align__(16) uint8_t tnq_gemv_smem[];
-  const uint32_t xs = smem_u32(tnq_gemv_smem);       // x as f16x2 (padded to whole warps), shared-space address
-  const uint32_t fx = xs + gemv_x_bytes<FP4>(k);     // x block factors (fp32), shared-space address
-  const uint32_t kb = k / F::kBlock;
-  float* partial = reinterpret_cast<float*>(tnq_gemv_smem + gemv_x_bytes<FP4>(k)) + ((kb + 3) & ~3u);  // [2][warps][rows]
   const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t team = warp / T, tlane = (warp % T) * 32 + lane;
+  const uint32_t ring = smem_u32(tnq_gemv_smem) + warp * (S * kSlotBytes) + lane * 16;  // this lane's ring
+  const uint32_t xs = smem_u32(tnq_gemv_smem) + kGemvWarps * S * kSlotBytes;             // x as f16x2 (whole warps)
+  const uint32_t fx = xs + gemv_x_bytes<FP4>(k);                                         // x block factors (fp32)
+  const uint32_t kb = k / F::kBlock;
 
   // ---- prologue: decode x once per CTA.  Piece q of chunk c is stored at uint4 index
   // (c / 32) * 32 * Q + q * 32 + (c % 32), so that the 32 lanes of a warp read consecutive
@@ -187,25 +204,24 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
   float g = 1.0f;
   if constexpr (FP4) g = (x_global ? *x_global : 1.0f) * (w_global ? *w_global : 1.0f);
 
-  // ---- this CTA's work: a balanced contiguous range of row groups, kTeams groups per round;
-  // every team runs the same number of rounds so that the CTA-wide barrier stays uniform.
+  // ---- this warp's work: a balanced contiguous range of row groups.
   // Group g owns rows (g / 32) * 128 + (g % 32) + 32 * r, r = 0..3.
   const uint32_t row_bytes = k / F::kElemsPerByte;
-  const uint32_t chunks = row_bytes / 16;                  // 16-byte chunks per row
-  const uint32_t steps = (chunks + T * 32 - 1) / (T * 32);  // steps per round (the last may be ragged)
+  const uint32_t chunks = row_bytes / 16;     // 16-byte chunks per row
+  const uint32_t steps = (chunks + 31) / 32;  // 512-byte steps per row (the last may be ragged)
   const uint32_t groups = ((n + 127) / 128) * 32;
-  const uint32_t g_begin = (uint32_t)((uint64_t)blockIdx.x * groups / gridDim.x);
-  const uint32_t g_end = (uint32_t)((uint64_t)(blockIdx.x + 1) * groups / gridDim.x);
-  const uint32_t rounds = (g_end - g_begin + kTeams - 1) / kTeams;
-  const uint32_t items = rounds * steps;
+  const uint32_t warps = gridDim.x * kGemvWarps, gw = blockIdx.x * kGemvWarps + warp;
+  const uint32_t g_begin = (uint32_t)((uint64_t)gw * groups / warps);
+  const uint32_t g_end = (uint32_t)((uint64_t)(gw + 1) * groups / warps);
+  const uint32_t items = (g_end - g_begin) * steps;
   const bool swz = layout == TNQ_SCALES_SWIZZLED;
-  const uint32_t kb0 = FP4 ? 2 * tlane : tlane >> 1;  // first block column of this lane's chunk in step 0
-  const uint32_t kb_step = FP4 ? 2 * T * 32 : T * 16;  // block columns a step advances
-  const uint32_t sh = swz ? (kb0 & 3) * 8 : 0;          // where this lane's scale byte(s) sit in a word of `sv`
+  const uint32_t kb0 = FP4 ? 2 * lane : lane >> 1;  // first block column of this lane's chunk in step 0
+  const uint32_t kb_step = FP4 ? 64 : 16;           // block columns a step advances
+  const uint32_t sh = swz ? (kb0 & 3) * 8 : 0;      // where this lane's scale byte(s) sit in a scale word
   const uint32_t ktiles = (kb + 3) >> 2;
 
-  // load cursor: the group's (clamped) rows and scale base, the lane's chunk and block column
-  uint32_t l_group = g_begin + team, l_step = 0, l_c = tlane, l_kb = kb0, l_item = 0;
+  // producer cursor: the group's (clamped) rows and scale base, the lane's chunk and block column
+  uint32_t l_group = g_begin, l_step = 0, l_c = lane, l_kb = kb0, l_item = 0, l_slot = 0;
   uint32_t l_row[kGemvRows];
   const uint8_t* l_sf = w_sf;
   auto enter_group = [&]() {
@@ -215,27 +231,33 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
     if (swz) l_sf = w_sf + ((uint64_t)(row0 >> 7) * ktiles) * 512 + (row0 & 31) * 16;
   };
   enter_group();
-  auto load = [&](GemvLoads& b) {
-    if (l_group < g_end && l_c < chunks) {
-      const uint8_t* wp = w + (uint64_t)l_c * 16;
+  uint4 sv_next = make_uint4(0, 0, 0, 0);  // raw layout: the scale bytes of the step after the one being consumed
+  auto load_raw_scales = [&](uint32_t group, uint32_t kbcol, uint32_t c) {
+    uint32_t v[kGemvRows] = {0, 0, 0, 0};
+    if (group < g_end && c < chunks) {
+      const uint32_t row0 = (group >> 5) * 128 + (group & 31);
 #pragma unroll
-      for (int r = 0; r < kGemvRows; ++r) b.w[r] = ldg128(wp + (uint64_t)l_row[r] * row_bytes);
-      if (swz) {  // one 16-byte piece: word r = row r's four block columns
-        b.sv = *reinterpret_cast<const uint4*>(l_sf + (uint64_t)(l_kb >> 2) * 512);
-      } else {
-        const uint8_t* sp = w_sf + l_kb;
-        uint32_t v[kGemvRows];
-#pragma unroll
-        for (int r = 0; r < kGemvRows; ++r) {
-          if constexpr (FP4) v[r] = *reinterpret_cast<const uint16_t*>(sp + (uint64_t)l_row[r] * kb);
-          else v[r] = sp[(uint64_t)l_row[r] * kb];
-        }
-        b.sv = make_uint4(v[0], v[1], v[2], v[3]);
+      for (int r = 0; r < kGemvRows; ++r) {
+        const uint8_t* sp = w_sf + (uint64_t)min(row0 + 32 * r, n - 1) * kb + kbcol;
+        if constexpr (FP4) v[r] = *reinterpret_cast<const uint16_t*>(sp);
+        else v[r] = *sp;
       }
     }
-    ++l_item, l_c += T * 32, l_kb += kb_step;
+    return make_uint4(v[0], v[1], v[2], v[3]);
+  };
+  auto issue = [&]() {  // one commit group per item, empty when there is nothing to fetch
+    if (l_item < items && l_c < chunks) {
+      const uint32_t slot = ring + l_slot * kSlotBytes;
+      const uint8_t* wp = w + (uint64_t)l_c * 16;
+#pragma unroll
+      for (int r = 0; r < kGemvRows; ++r) cp_async16(slot + r * 512, wp + (uint64_t)l_row[r] * row_bytes);
+      if (swz) cp_async16(slot + kGemvRows * 512, l_sf + (uint64_t)(l_kb >> 2) * 512);
+    }
+    cp_async_commit();
+    ++l_item, l_c += 32, l_kb += kb_step;
+    if (++l_slot == S) l_slot = 0;
     if (++l_step == steps) {
-      l_step = 0, l_c = tlane, l_kb = kb0, l_group += kTeams;
+      l_step = 0, l_c = lane, l_kb = kb0, ++l_group;
       enter_group();
     }
   };
@@ -243,11 +265,13 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
   float acc[kGemvRows];
 #pragma unroll
   for (int r = 0; r < kGemvRows; ++r) acc[r] = 0.0f;
-  uint32_t c_group = g_begin + team, c_step = 0, c_c = tlane;
-  uint32_t xi = (tlane >> 5) * Q * 32 + lane;  // uint4 index of this lane's first x piece
-  auto consume = [&](const GemvLoads& b) {
-    if (c_group >= g_end || c_c >= chunks) return;
-    const uint32_t sw[kGemvRows] = {b.sv.x >> sh, b.sv.y >> sh, b.sv.z >> sh, b.sv.w >> sh};
+  uint32_t c_group = g_begin, c_step = 0, c_c = lane, c_kb = kb0, c_slot = 0;
+  uint32_t xi = lane;  // uint4 index of this lane's first x piece
+  auto consume = [&](const uint4& sv_raw) {
+    if (c_c >= chunks) return;
+    const uint32_t slot = ring + c_slot * kSlotBytes;
+    const uint4 sv = swz ? lds128(slot + kGemvRows * 512) : sv_raw;
+    const uint32_t sw[kGemvRows] = {sv.x >> sh, sv.y >> sh, sv.z >> sh, sv.w >> sh};
     if constexpr (FP4) {
       uint4 xv[4];
 #pragma unroll
@@ -256,7 +280,8 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
       const uint32_t fxh = half2_as_u32(__floats2half2_rn(fxv.x, fxv.y));  // e4m3 values: exact in fp16
 #pragma unroll
       for (int r = 0; r < kGemvRows; ++r) {
-        const uint32_t wr[4] = {b.w[r].x, b.w[r].y, b.w[r].z, b.w[r].w};
+        const uint4 wv = lds128(slot + r * 512);
+        const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
         float s0, s1;  // x factor * row scale of the two blocks, exact
         mul2_f16_f32(cvt_e4m3x2_to_f16x2(sw[r]), fxh, s0, s1);
         float p[2];
@@ -284,11 +309,12 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
       const float f = lds32f(fx + (c_c >> 1) * 4);
 #pragma unroll
       for (int r = 0; r < kGemvRows; ++r) {
+        const uint4 wv = lds128(slot + r * 512);
         uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-        cvt_e4m3x4_to_f16x2(b.w[r].x, a0, a1);
-        cvt_e4m3x4_to_f16x2(b.w[r].y, a2, a3);
-        cvt_e4m3x4_to_f16x2(b.w[r].z, b0, b1);
-        cvt_e4m3x4_to_f16x2(b.w[r].w, b2, b3);
+        cvt_e4m3x4_to_f16x2(wv.x, a0, a1);
+        cvt_e4m3x4_to_f16x2(wv.y, a2, a3);
+        cvt_e4m3x4_to_f16x2(wv.z, b0, b1);
+        cvt_e4m3x4_to_f16x2(wv.w, b2, b3);
         float p = 0.0f, q = 0.0f;  // two chains per row
         p = fma2_f16_f32(a0, xa.x, p);
         q = fma2_f16_f32(b0, xb.x, q);
@@ -302,63 +328,48 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
       }
     }
   };
-  uint32_t par = 0;
-  auto finish = [&]() {  // end of a round: fold lanes, then the team's warps, store
+  auto step_done = [&]() {
+    c_c += 32, c_kb += kb_step, xi += Q * 32;
+    if (++c_slot == S) c_slot = 0;
+    if (++c_step == steps) {  // end of the group: fold the lanes, lane r stores row r
 #pragma unroll
-    for (int r = 0; r < kGemvRows; ++r) {
-      float v = acc[r];
+      for (int r = 0; r < kGemvRows; ++r) {
+        float v = acc[r];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      acc[r] = v;
-    }
-    const uint32_t row = (c_group >> 5) * 128 + (c_group & 31) + 32 * lane;  // lane r stores row r
-    const bool store = lane < kGemvRows && c_group < g_end && row < n;
-    if constexpr (T == 1) {
-      if (store) {
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        acc[r] = v;
+      }
+      const uint32_t row = (c_group >> 5) * 128 + (c_group & 31) + 32 * lane;
+      if (lane < kGemvRows && row < n) {
         float v = acc[0];
 #pragma unroll
         for (int r = 1; r < kGemvRows; ++r) v = lane == r ? acc[r] : v;
         y[row] = __bfloat16_as_ushort(__float2bfloat16_rn(FP4 ? __fmul_rn(v, g) : v));
       }
-    } else {
-      float* mine = partial + (par * kGemvWarps + warp) * kGemvRows;
-      if (lane == 0) {
 #pragma unroll
-        for (int r = 0; r < kGemvRows; ++r) mine[r] = acc[r];
-      }
-      __syncthreads();
-      if (warp % T == 0 && store) {
-        float v = 0.0f;
-#pragma unroll
-        for (int j = 0; j < T; ++j) v += partial[(par * kGemvWarps + warp + j) * kGemvRows + lane];
-        y[row] = __bfloat16_as_ushort(__float2bfloat16_rn(FP4 ? __fmul_rn(v, g) : v));
-      }
-      par ^= 1u;  // the other buffer is free again once every warp has passed the next barrier
-    }
-#pragma unroll
-    for (int r = 0; r < kGemvRows; ++r) acc[r] = 0.0f;
-  };
-  auto step_done = [&]() {
-    c_c += T * 32, xi += T * Q * 32;
-    if (++c_step == steps) {
-      finish();
-      c_step = 0, c_c = tlane, xi = (tlane >> 5) * Q * 32 + lane, c_group += kTeams;
+      for (int r = 0; r < kGemvRows; ++r) acc[r] = 0.0f;
+      c_step = 0, c_c = lane, c_kb = kb0, xi = lane, ++c_group;
     }
   };
 
-  // ---- the pipeline: the next step's loads are in flight while this one is consumed
-  GemvLoads buf[2];
-  if (items > 0) load(buf[0]);
-  for (uint32_t it = 0; it < items; it += 2) {
-    if (l_item < items) load(buf[1]);
-    consume(buf[0]);
-    step_done();
-    if (it + 1 < items) {
-      if (l_item < items) load(buf[0]);
-      consume(buf[1]);
-      step_done();
+  // ---- the pipeline
+#pragma unroll
+  for (int d = 0; d < S - 1; ++d) issue();
+  uint4 sv_cur = make_uint4(0, 0, 0, 0);
+  if (!swz) sv_cur = load_raw_scales(c_group, c_kb, c_c);
+  for (uint32_t it = 0; it < items; ++it) {
+    issue();  // refills the slot consumed in the previous iteration
+    if (!swz) {  // raw scale bytes cannot go through 16-byte copies: keep them one step ahead in registers
+      uint32_t ng = c_group, nk = c_kb + kb_step, nc = c_c + 32;
+      if (c_step + 1 == steps) ng = c_group + 1, nk = kb0, nc = lane;
+      sv_next = load_raw_scales(ng, nk, nc);
     }
+    cp_async_wait<S - 1>();  // everything but the S - 1 newest groups has landed: this item's slot is ready
+    consume(sv_cur);
+    step_done();
+    sv_cur = sv_next;
   }
+  cp_async_wait<0>();
 }
 
 }  // namespace tnq
@@ -366,48 +377,34 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
 using namespace tnq;
 using namespace tnq_host;
 
-template <bool FP4, int T>
-static int launch_gemv_t(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg,
-                         const float* wg, int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
+template <bool FP4>
+static int launch_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg, const float* wg,
+                       int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
   using F = GemvFmt<FP4>;
-  constexpr int kTeams = kGemvWarps / T;
   const int kb = (int)(k / F::kBlock);
-  const int smem = gemv_x_bytes<FP4>((int)k) + ((kb + 3) & ~3) * 4 + 2 * kGemvWarps * kGemvRows * 4;
+  const int smem = kGemvWarps * kGemvStages * kSlotBytes + gemv_x_bytes<FP4>((int)k) + ((kb + 3) & ~3) * 4;
   static int configured[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) !=
+    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
         cudaSuccess)
       return cuda_fail(cudaGetLastError());
     configured[dev] = 1;
   }
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_blockscaled_gemv<FP4, T>, kGemvThreads, smem) !=
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_blockscaled_gemv<FP4>, kGemvThreads, smem) !=
           cudaSuccess ||
       per_sm < 1)
     return TNQ_EUNSUPPORTED;
   const int64_t groups = ((n + 127) / 128) * 32;
-  const int64_t want = (groups + kTeams - 1) / kTeams;
+  const int64_t want = (groups + kGemvWarps - 1) / kGemvWarps;
   const int64_t cap = (int64_t)per_sm * sm_count();
   const int grid = (int)(want < cap ? want : cap);
-  k_blockscaled_gemv<FP4, T><<<grid, kGemvThreads, smem, stream>>>(
+  k_blockscaled_gemv<FP4><<<grid, kGemvThreads, smem, stream>>>(
       static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(x_sf),
       static_cast<const uint8_t*>(w_sf), xg, wg, (uint32_t)n, (uint32_t)k, layout, static_cast<uint16_t*>(y));
   return check_launch();
-}
-
-// Team size.  One warp per row group keeps every warp independent (no CTA barrier) and is
-// the fastest once a row spans at least one 512-byte step; shorter rows share a warp's lanes
-// poorly either way.
-template <bool FP4>
-static int launch_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg, const float* wg,
-                       int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
-#ifdef TNQ_GEMV_FORCE_T
-  return launch_gemv_t<FP4, TNQ_GEMV_FORCE_T>(x, w, x_sf, w_sf, xg, wg, n, k, layout, y, stream);
-#else
-  return launch_gemv_t<FP4, 1>(x, w, x_sf, w_sf, xg, wg, n, k, layout, y, stream);
-#endif
 }
 
 extern "C" int tnq_mxfp8_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, int64_t n, int64_t k,
