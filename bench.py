@@ -394,6 +394,11 @@ def run_ours(args):
     base = None
     if rank == 0 and world == 1 and not args.no_cpu:
         base, _ = cpu_baseline(HEADLINE, 3, 1, cfg.rows // 8)
+        if extras is not None:  # the oracle port beside every other configuration, on a bounded row sample
+            for name, rows in (("fp8_tensor", 4096), ("fp8_rowwise", 2048), ("mxfp8", 1024), ("nvfp4", 512)):
+                if name in extras:
+                    b, _ = cpu_baseline(name, 2, 1, rows)
+                    extras[name]["cpu_port"] = {"GBps": b["value"], "cores": b["cores"], "sample": b["sample"]}
 
     if exchange is not None:
         exchange.close()
@@ -431,7 +436,21 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
     def timed(fn, sets, n_it=30, n_warm=5):
         n_it = iters if iters is not None else n_it
         n_warm = warm if warm is not None else n_warm
-        return _timed(fn, sets, n_it, n_warm)
+        ms = _timed(fn, sets, n_it, n_warm)
+        timed.last_distribution = _per_launch(fn, sets, 100) if iters is None else None
+        return ms
+
+    def _per_launch(fn, sets, n):
+        """One CUDA-event pair around every launch (includes the idle-queue launch latency,
+        a few microseconds): median, 5th and 95th percentile in microseconds."""
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for i, (a, b) in enumerate(ev):
+            a.record()
+            fn(sets[i % len(sets)])
+            b.record()
+        torch.cuda.synchronize()
+        t = sorted(a.elapsed_time(b) * 1e3 for a, b in ev)
+        return {"median": t[n // 2], "p05": t[n // 20], "p95": t[(19 * n) // 20], "launches": n}
 
     def _timed(fn, sets, iters, warm):
         for i in range(warm):
@@ -452,8 +471,11 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         cfg = CONFIGS[name]
         bpe = cfg.algo_bytes_per_elem if bytes_per_elem is None else bytes_per_elem
         gbs = bpe * cfg.rows * cfg.cols / (ms * 1e-3) / 1e9
-        return {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
-                "algorithmic_bytes_per_element": bpe, "note": note}
+        r = {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+             "algorithmic_bytes_per_element": bpe, "note": note}
+        if getattr(timed, "last_distribution", None):
+            r["per_launch_us"] = timed.last_distribution
+        return r
 
     def want(name):
         return only is None or only == name
@@ -487,8 +509,11 @@ def _bench_gemv(dev, res, timed, peak, stream, which=None):
 
     def report(us, nbytes, note):
         gbs = nbytes / (us * 1e-6) / 1e9
-        return {"us": us, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
-                "algorithmic_bytes": nbytes, "note": note}
+        r = {"us": us, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+             "algorithmic_bytes": nbytes, "note": note}
+        if getattr(timed, "last_distribution", None):
+            r["per_launch_us"] = timed.last_distribution
+        return r
 
     if which in (None, "gemv_mxfp8"):
         n, k = 32768, 8192
@@ -541,7 +566,36 @@ def _bench_fp8_tensor(dev, res, timed, report, ws, stream):
 
     res["fp8_tensor"] = report("fp8_tensor", timed(f1, sets, 64, 16), "cold L2: 8 rotating buffer sets")
     res["fp8_tensor_hot_l2"] = report("fp8_tensor", timed(f1, sets[:1], 64, 16), "hot L2: one buffer set")
-    del sets
+
+    # the same eight calls replayed from one CUDA graph (launch overhead out of the picture)
+    side = torch.cuda.Stream()
+    gws = torch.zeros(_lib.WORKSPACE_BYTES // 4, dtype=torch.int32, device=dev)
+
+    def all_sets():
+        for s in sets:
+            _lib.call("tnq_fp8_dynamic_cast", s[0].data_ptr(), s[1].data_ptr(), s[0].numel(), _lib.IN_BF16,
+                      _lib.FP8_E4M3, gws.data_ptr(), 0, side.cuda_stream)
+
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        all_sets()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        all_sets()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(8):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    res["fp8_tensor_graph_replay"] = report("fp8_tensor", e0.elapsed_time(e1) / 64,
+                                            "cold L2, eight calls per CUDA graph, eight replays")
+    res["fp8_tensor_graph_replay"].pop("per_launch_us", None)
+    del sets, graph
 
 
 def _bench_rowwise(dev, res, timed, report, stream):

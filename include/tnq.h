@@ -89,6 +89,21 @@ int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int o
                         const float* scale, int scale_source, int saturated,
                         float* abs_max_inout, void* workspace, tnq_stream_t stream);
 
+/* Delayed-scaling state update between two steps, for `tensors` tensors in one launch.
+ * amax_history is fp32 [tensors, history_len], newest first; amax and scale are fp32
+ * [tensors].  For every t: the history is shifted by one (oldest dropped),
+ * history[t][0] = amax[t], scale[t] = fp8_max / max(max over history[t], 1e-12) (a NaN in
+ * the history gives a NaN scale), amax[t] = 0.  history_len <= 1024.
+ * amax[t] is what `tnq_fp8_scaled_cast` accumulates through abs_max_inout during the step;
+ * scale[t] is what the next step passes as its scale.
+ * The reference leaves this step to float8_experimental's
+ * `sync_float8_amax_and_scale_history` (called from llama/train.py:251-263; the package is
+ * not part of the reference tree and is not version-pinned by it); this follows that
+ * function's published "max" recipe: roll the history, take its maximum, scale =
+ * fp8_max / clamp(amax, 1e-12). */
+int tnq_delayed_scale_update(float* amax_history, float* amax, float* scale, int64_t tensors,
+                             int history_len, int out_dtype, tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent

@@ -18,6 +18,7 @@ Parity status of each function is stated in its docstring:
 
 from .cast_oracle import (  # noqa: F401
     FP8_MAX,
+    delayed_scale_update,
     e2m1_decode,
     e2m1_encode,
     e8m0_exponent_ceil_int,

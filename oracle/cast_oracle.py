@@ -110,6 +110,22 @@ def fp8_rowwise_quant(a: torch.Tensor, fp8_dtype: torch.dtype):
     return out.to(fp8_dtype), scale
 
 
+def delayed_scale_update(amax_history: torch.Tensor, amax: torch.Tensor, fp8_dtype: torch.dtype):
+    """Delayed-scaling state update for a stack of tensors: returns (new history
+    [T, L], new scale [T]).  ``history <- roll(history, 1, dim=1); history[:, 0] = amax;
+    scale = finfo.max / clamp(max(history, dim=1), 1e-12)`` in fp32.
+
+    Parity: UNPINNED restatement.  The reference calls float8_experimental's
+    ``sync_float8_amax_and_scale_history`` (llama/train.py:251-263); that package is not in
+    the reference tree and its version is not pinned by pyproject.toml.  This follows its
+    published "max" recipe (``_update_history_stack`` + ``amax_history_to_scale_stack``)
+    with the single fp32 division the other casts use.
+    """
+    hist = torch.roll(amax_history.to(torch.float32), 1, dims=1)
+    hist[:, 0] = amax.to(torch.float32).reshape(-1)
+    return hist, _scale_from_amax(hist.max(dim=1).values, fp8_dtype)
+
+
 def sharded_fp8_dynamic_quant(shards, fp8_dtype: torch.dtype):
     """Row-sharded per-tensor cast: local amax -> MAX over shards -> same scale
     on every shard -> cast.  Returns (list of fp8 shards, scale [1]).

@@ -4,3 +4,4 @@ from .scaled_quant import (  # noqa: F401
     rowwise_scaled_quant,
     scaled_quant,
 )
+from .delayed_scaling import DelayedScaling, combine_amaxes  # noqa: F401
