@@ -488,12 +488,56 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_mxfp8(dev, res, timed, report, ws, stream)
     if want("nvfp4"):
         _bench_nvfp4(dev, res, timed, report, ws, stream)
+    if want("fp8_transpose"):
+        _bench_transpose(dev, res, timed, peak, ws, stream)
     if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
         _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
     st = int(ws[_lib.WS_STATUS_WORD].item())
     if st != 0:
         raise SystemExit(f"device status word {st}: a bounded wait expired in a tile kernel")
     return res
+
+
+def _bench_transpose(dev, res, timed, peak, ws, stream):
+    """Per-tensor e4m3 cast that also writes the transposed copy (bf16 16384 x 8192, 256 MiB in):
+    delayed scale with the abs_max side output (2 + 1 + 1 B/elem) and dynamic scale (amax pass
+    first: 2 more B/elem, the tensor is larger than L2)."""
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
+    x = make_input("fp8_rowwise", dev)
+    rows, cols = x.shape
+    q = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    q_t = torch.empty(cols, rows, dtype=torch.float8_e4m3fn, device=dev)
+    scale = torch.full((1,), 0.5, dtype=torch.float32, device=dev)
+    am = torch.zeros(1, dtype=torch.float32, device=dev)
+    status = ws.data_ptr() + 4 * _lib.WS_STATUS_WORD
+
+    def report(ms, bpe, note):
+        gbs = bpe * rows * cols / (ms * 1e-3) / 1e9
+        r = {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+             "algorithmic_bytes_per_element": bpe, "note": note}
+        if getattr(timed, "last_distribution", None):
+            r["per_launch_us"] = timed.last_distribution
+        return r
+
+    def delayed(_):
+        _lib.call("tnq_fp8_cast_transpose", x.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_E4M3, scale.data_ptr(),
+                  _lib.SCALE_IS_SCALE, 1, am.data_ptr(), q.data_ptr(), q_t.data_ptr(), status, stream)
+
+    def dynamic(_):
+        _lib.call("tnq_fp8_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), 0, stream)
+        _lib.call("tnq_fp8_cast_transpose", x.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_E4M3,
+                  ws.data_ptr() + 4 * _lib.WS_SCALE_WORD, _lib.SCALE_IS_SCALE, 1, 0, q.data_ptr(), q_t.data_ptr(), status,
+                  stream)
+
+    res["fp8_cast_transpose"] = report(timed(delayed, [None]), 4.0,
+                                       f"{rows}x{cols}, delayed scale + abs_max side output, both layouts from one read")
+    res["fp8_dynamic_cast_transpose"] = report(timed(dynamic, [None]), 6.0,
+                                               f"{rows}x{cols}, amax pass + transposing cast, input 256 MiB > L2")
+    del x, q, q_t
 
 
 def _bench_gemv(dev, res, timed, peak, stream, which=None):

@@ -104,6 +104,19 @@ int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int o
 int tnq_delayed_scale_update(float* amax_history, float* amax, float* scale, int64_t tensors,
                              int history_len, int out_dtype, tnq_stream_t stream);
 
+/* Per-tensor scaled cast of a bf16 [rows, cols] matrix that also writes the transposed
+ * copy, from one read: out [rows, cols] = fp8(x * s), out_t [cols, rows] = out^T.  Scale
+ * argument, saturation and overflow semantics and the abs_max side output exactly as in
+ * tnq_fp8_scaled_cast (abs_max_inout is updated with an atomic max and needs no workspace;
+ * it must hold a non-negative value or NaN on entry).  cols % 8 == 0; out_t is written with
+ * 32-byte stores when rows % 32 == 0 and out_t is 32-byte aligned, else byte by byte.
+ * `status` (nullable) receives TNQ_ETIMEOUT if a bounded wait on a tile load gives up.
+ * No counterpart in the reference: its casts (fp8/scaled_quant.py:35-75, 139-169) produce one
+ * layout; the transposed operand of the backward GEMM is left to the caller. */
+int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
+                           const float* scale, int scale_kind, int saturated, float* abs_max_inout,
+                           void* out, void* out_t, uint32_t* status, tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent

@@ -1,0 +1,209 @@
+// Per-tensor scaled FP8 cast that also emits the transposed copy:
+//     out[r, c] = fp8(x[r, c] * s)        row-major [rows, cols]
+//     out_t[c, r] = out[r, c]             row-major [cols, rows]
+// from ONE read of x.  An FP8 training step needs both layouts of the same tensor (the
+// forward GEMM contracts over one dimension, the weight-gradient GEMM over the other); done
+// separately that is a cast (2 + 1 B/elem) plus a transpose (1 + 1 B/elem), here it is
+// 2 + 1 + 1.  Same arithmetic as the plain cast (fp8_tensor.cu): y = f32(x) * s as one fp32
+// product, optional saturation, RNE cvt, the CPU cast's NaN / overflow corner cases; the two
+// outputs hold identical bytes.  Optional side output: abs_max = max(abs_max, max|x|) for
+// delayed scaling.
+//
+// 128 x 128 bf16 tiles arrive by 2-D TMA into a three-stage mbarrier ring.  Threads 0-255
+// make the row-major output, threads 256-511 the transposed output.  Each element is converted twice rather than staged through a second
+// shared-memory tile: the conversions are cheap and the kernel is bound by its three
+// global streams.
+#include "tile_pipeline.cuh"
+
+namespace tnq {
+
+struct CastTParams {
+  int64_t rows, cols;
+  const float* scale;
+  int scale_kind;
+  float* abs_max;  // nullable
+  uint8_t* out;
+  uint8_t* out_t;
+  int t_aligned;  // rows % 32 == 0: every 32-row run of out_t starts on a 32-byte boundary
+};
+
+// 16 bytes of bf16 -> 8 bytes of fp8 per thread and row; a warp writes two 128-byte row
+// segments.  `m` collects the magnitude bits of everything the thread saw.
+template <int OUT, bool SAT, bool FULL>
+__device__ __forceinline__ void ct_row_pass(const CastTParams& p, float s, uint32_t& m, uint32_t tile, uint32_t tr,
+                                            uint32_t tc, int t) {
+  const int piece = t & 15, r_in = t >> 4;
+  const int64_t c = (int64_t)tc * kTileCols + piece * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = i * 16 + r_in;
+    const int64_t r = (int64_t)tr * kTileRows + row;
+    const uint4 v = lds128(tile + row * 256 + piece * 16);  // zeros outside the matrix
+    m = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m, v.x), v.y), v.z), v.w);
+    if (FULL || (r < p.rows && c < p.cols)) stg64(p.out + r * p.cols + c, quant8_bf16<OUT, SAT>(v, s));
+  }
+}
+
+// A thread owns two adjacent columns over 32 rows: 32 conflict-free 4-byte shared loads, one
+// 32-byte store per column of the transposed output.
+template <int OUT, bool SAT, bool FULL>
+__device__ __forceinline__ void ct_col_pass(const CastTParams& p, float s, uint32_t tile, uint32_t tr, uint32_t tc,
+                                            int u) {
+  const int w = u & 63, rb = u >> 6;
+  const uint32_t src = tile + rb * 32 * 256 + w * 4;
+  uint32_t v[32];
+  static_for<32>([&](auto I) {
+    constexpr int i = decltype(I)::value;
+    v[i] = lds32_at<i * 256>(src);
+  });
+  uint32_t lo[8], hi[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    lo[j] = quant4<OUT, SAT>(bf16lo(v[4 * j]), bf16lo(v[4 * j + 1]), bf16lo(v[4 * j + 2]), bf16lo(v[4 * j + 3]), s);
+    hi[j] = quant4<OUT, SAT>(bf16hi(v[4 * j]), bf16hi(v[4 * j + 1]), bf16hi(v[4 * j + 2]), bf16hi(v[4 * j + 3]), s);
+  }
+  const int64_t c = (int64_t)tc * kTileCols + 2 * w;
+  const int64_t r0 = (int64_t)tr * kTileRows + rb * 32;
+  if (FULL || (c < p.cols && r0 < p.rows)) {  // cols is even, so column c + 1 exists with column c
+    uint8_t* d0 = p.out_t + c * p.rows + r0;
+    if (p.t_aligned && (FULL || r0 + 32 <= p.rows)) {
+      stg256(d0, lo[0], lo[1], lo[2], lo[3], lo[4], lo[5], lo[6], lo[7]);
+      stg256(d0 + p.rows, hi[0], hi[1], hi[2], hi[3], hi[4], hi[5], hi[6], hi[7]);
+    } else {  // ragged or unaligned rows: byte stores
+      const int nr = (int)min((int64_t)32, p.rows - r0);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i < nr) {
+          d0[i] = (uint8_t)(lo[i >> 2] >> (8 * (i & 3)));
+          d0[p.rows + i] = (uint8_t)(hi[i >> 2] >> (8 * (i & 3)));
+        }
+      }
+    }
+  }
+}
+
+// The two groups walk the tile sequence at their own pace (as in the MXFP8 row + column
+// kernel): a group waits only for the tile's mbarrier and for its own members (named
+// barrier); whichever group releases a stage second re-arms it and issues the next load.
+template <int OUT, bool SAT>
+__global__ void __launch_bounds__(512, 2)
+    k_cast_transpose(const __grid_constant__ CUtensorMap tmap, CastTParams p, uint32_t tiles_r, uint32_t tiles_c,
+                     uint32_t* status) {
+  extern __shared__ uint8_t tnq_dyn_smem[];
+  uint8_t* const base = tile_smem_base(tnq_dyn_smem);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(base + kStages * kTileBytes);       // kStages x 8 bytes
+  uint32_t* const done = reinterpret_cast<uint32_t*>(base + kStages * kTileBytes + 32);  // kStages x 4 bytes
+  uint32_t* const cta_max = done + kStages;                                              // one word
+  const uint32_t tile0 = smem_u32(base);
+  const uint32_t ntiles = tiles_r * tiles_c;
+  const uint32_t first = blockIdx.x;
+  const uint32_t count = first < ntiles ? (ntiles - first + gridDim.x - 1) / gridDim.x : 0;
+  const int group = threadIdx.x >> 8, gtid = threadIdx.x & 255;
+
+  TileCursor cur, ahead;
+  cur.init(first, gridDim.x, tiles_c);
+  ahead = cur;
+  auto issue = [&](uint32_t s) {  // one thread: arm stage s and load the tile at `ahead` into it
+    mbar_expect_tx(&bars[s], kTileBytes);
+    tma_load_2d(base + s * kTileBytes, &tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s]);
+  };
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars[s], 1);
+      done[s] = 0;
+    }
+    *cta_max = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {  // every thread keeps `ahead` kStages tiles in front of `cur`
+    if (threadIdx.x == 0 && s < count) issue(s);
+    ahead.advance();
+  }
+  const float v = *p.scale;
+  const float scale = p.scale_kind == TNQ_SCALE_IS_AMAX ? scale_from_amax(v, Fp8Traits<OUT>::kMax) : v;
+  uint32_t m = 0;
+
+  uint32_t s = 0, phase = 0;
+  for (uint32_t k = 0; k < count; ++k) {
+    if (!mbar_wait(&bars[s], phase)) {
+      if (gtid == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_ETIMEOUT);
+      return;
+    }
+    const uint32_t tile = tile0 + s * kTileBytes;
+    const bool full = (int64_t)(cur.tr + 1) * kTileRows <= p.rows && (int64_t)(cur.tc + 1) * kTileCols <= p.cols;
+    if (group == 0) {
+      if (full) ct_row_pass<OUT, SAT, true>(p, scale, m, tile, cur.tr, cur.tc, gtid);
+      else ct_row_pass<OUT, SAT, false>(p, scale, m, tile, cur.tr, cur.tc, gtid);
+      named_barrier<1, 256>();
+    } else {
+      if (full) ct_col_pass<OUT, SAT, true>(p, scale, tile, cur.tr, cur.tc, gtid);
+      else ct_col_pass<OUT, SAT, false>(p, scale, tile, cur.tr, cur.tc, gtid);
+      named_barrier<2, 256>();
+    }
+    if (gtid == 0) {
+      __threadfence_block();
+      if (atomicAdd(&done[s], 1u) == 1u) {  // the other group released the stage earlier: reuse it
+        atomicExch(&done[s], 0u);
+        if (k + kStages < count) issue(s);  // `ahead` is the tile kStages after `cur`
+      }
+    }
+    cur.advance();
+    ahead.advance();
+    if (++s == (uint32_t)kStages) s = 0, phase ^= 1u;
+  }
+  // max|x| of everything the row group saw -> abs_max (integer-ordered: non-negative floats, NaN on top)
+  if (p.abs_max != nullptr && group == 0) {
+    const uint32_t wm = warp_max_u32(fold_u16x2(m));
+    if ((gtid & 31) == 0 && wm != 0u) atomicMax(cta_max, wm);
+    named_barrier<1, 256>();
+    if (gtid == 0 && *cta_max != 0u) atomicMax(reinterpret_cast<uint32_t*>(p.abs_max), *cta_max << 16);
+  }
+}
+
+}  // namespace tnq
+
+using namespace tnq;
+using namespace tnq_host;
+
+template <int OUT, bool SAT>
+static int launch_cast_transpose(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
+  const int cap = tile_resident_ctas<k_cast_transpose<OUT, SAT>, 512>();
+  if (cap < 1) return cuda_fail(cudaGetLastError());
+  const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
+  const int64_t ntiles = tiles_r * tiles_c;
+  const int grid = (int)(ntiles < cap ? ntiles : cap);
+  k_cast_transpose<OUT, SAT><<<grid, 512, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
+  return check_launch();
+}
+
+extern "C" int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
+                                      const float* scale, int scale_kind, int saturated, float* abs_max_inout,
+                                      void* out, void* out_t, uint32_t* status, tnq_stream_t stream) {
+  if (rows < 0 || cols < 0) return TNQ_EINVAL;
+  if (in_dtype != TNQ_IN_BF16) return TNQ_EUNSUPPORTED;
+  if (out_dtype != TNQ_FP8_E4M3 && out_dtype != TNQ_FP8_E5M2) return TNQ_EINVAL;
+  if (scale_kind != TNQ_SCALE_IS_SCALE && scale_kind != TNQ_SCALE_IS_AMAX) return TNQ_EINVAL;
+  if (scale == nullptr) return TNQ_EINVAL;
+  if (rows == 0 || cols == 0) return TNQ_OK;
+  if (x == nullptr || out == nullptr || out_t == nullptr) return TNQ_EINVAL;
+  if (cols % 8 != 0) return TNQ_ESHAPE;  // 16-byte row pitch for the tile loads, 8-byte output pieces
+  if (rows > 0x7fffffff || cols > 0x7fffffff) return TNQ_EUNSUPPORTED;
+  if (((rows + 127) / 128) * ((cols + 127) / 128) > 0x7fffffff) return TNQ_EUNSUPPORTED;  // 32-bit tile cursor
+  if (!aligned16(x) || !aligned16(out)) return TNQ_EALIGN;
+  CUtensorMap map;
+  int rc = make_tile_map(&map, x, rows, cols);
+  if (rc != TNQ_OK) return rc;
+  CastTParams p;
+  p.rows = rows, p.cols = cols;
+  p.scale = scale, p.scale_kind = scale_kind;
+  p.abs_max = abs_max_inout;
+  p.out = static_cast<uint8_t*>(out), p.out_t = static_cast<uint8_t*>(out_t);
+  p.t_aligned = (rows % 32 == 0) && ((reinterpret_cast<uintptr_t>(out_t) & 31u) == 0);
+  if (out_dtype == TNQ_FP8_E4M3)
+    return saturated ? launch_cast_transpose<TNQ_FP8_E4M3, true>(map, p, status, stream)
+                     : launch_cast_transpose<TNQ_FP8_E4M3, false>(map, p, status, stream);
+  return saturated ? launch_cast_transpose<TNQ_FP8_E5M2, true>(map, p, status, stream)
+                   : launch_cast_transpose<TNQ_FP8_E5M2, false>(map, p, status, stream);
+}

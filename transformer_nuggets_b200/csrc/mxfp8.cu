@@ -228,6 +228,8 @@ struct MxOp {
     }
   }
 
+  __device__ static __forceinline__ void finish(const Params&, const State&) {}
+
   __device__ static __forceinline__ void flush(const Params& p, uint32_t sf, uint32_t tr, uint32_t tc) {
     if constexpr (ROW) flush_one(sf, p.sf_row, p.layout, p.rows, p.sf_row_w, tr, tc, 0, kThreads);
     if constexpr (COL) flush_one(sf + 512, p.sf_col, p.layout, p.cols, p.sf_col_w, tc, tr, 0, kThreads);

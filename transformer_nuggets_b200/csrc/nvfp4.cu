@@ -123,6 +123,8 @@ struct Fp4Op {
     }
   }
 
+  __device__ static __forceinline__ void finish(const Params&, const State&) {}
+
   __device__ static __forceinline__ void flush(const Params& p, uint32_t sf, uint32_t tr, uint32_t tc) {
     const int64_t ncb = (p.sf_w + 3) / 4;
     if (p.layout == TNQ_SCALES_SWIZZLED) {

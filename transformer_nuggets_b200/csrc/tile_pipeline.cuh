@@ -37,6 +37,8 @@ __device__ __forceinline__ uint8_t* tile_smem_base(uint8_t* raw) {
 //                                                all threads; tile / sf are 32-bit shared-space
 //                                                addresses; FULL = the tile lies inside the matrix
 // Op::flush(params, sf, tile_row, tile_col)      all threads, after a __syncthreads
+// Op::finish(params, state)                      all threads, after the last tile (state is mutable
+//                                                across tiles: running maxima live there)
 // Position of a CTA in its tile sequence (tiles blockIdx.x, + gridDim.x, ...), advanced
 // without divisions: 32-bit tile coordinates, the ring stage and its phase bit.
 struct TileCursor {
@@ -73,7 +75,7 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
     fence_mbar_init();
   }
   __syncthreads();
-  const typename Op::State state = Op::init(p);
+  typename Op::State state = Op::init(p);
   TileCursor cur, ahead;  // tile being consumed / next tile to load
   cur.init(first, gridDim.x, tiles_c);
   ahead = cur;
@@ -105,6 +107,7 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
     cur.advance();
     if (++s == (uint32_t)kStages) s = 0, phase ^= 1u;
   }
+  Op::finish(p, state);
 }
 
 }  // namespace tnq

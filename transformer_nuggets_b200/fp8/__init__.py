@@ -1,7 +1,9 @@
 from .scaled_quant import (  # noqa: F401
     dynamic_scaled_quant,
+    dynamic_scaled_quant_transpose,
     dynamic_scaled_quant_with_scale,
     rowwise_scaled_quant,
     scaled_quant,
+    scaled_quant_transpose,
 )
 from .delayed_scaling import DelayedScaling, combine_amaxes  # noqa: F401

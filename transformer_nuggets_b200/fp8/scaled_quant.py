@@ -85,6 +85,73 @@ def dynamic_scaled_quant_with_scale(
     return out, scale
 
 
+def _check_matrix(inpt_tensor: torch.Tensor):
+    _check_input(inpt_tensor)
+    if inpt_tensor.dim() != 2:
+        raise ValueError("the transposing casts take a 2-D tensor")
+    if inpt_tensor.dtype != torch.bfloat16:
+        raise TypeError("the transposing casts take bfloat16 input")
+    if inpt_tensor.shape[1] % 8 != 0:
+        raise ValueError("the number of columns must be a multiple of 8")
+
+
+def scaled_quant_transpose(
+    inpt_tensor: torch.Tensor,
+    scale: torch.Tensor,
+    abs_max: torch.Tensor | None = None,
+    fp8_dtype: torch.dtype = torch.float8_e4m3fn,
+    saturated: bool = False,
+):
+    """``scaled_quant`` of a 2-D bf16 tensor that also returns the transposed copy:
+    ``(q [R, C], q_t [C, R])`` with ``q_t == q.t().contiguous()`` byte for byte, from one
+    read of the input.  ``abs_max`` (optional, one fp32 element) becomes
+    ``max(abs_max, max|inpt_tensor|)`` as in ``scaled_quant``."""
+    _check_matrix(inpt_tensor)
+    _check_fp8(fp8_dtype)
+    assert scale.dtype == torch.float32 and scale.numel() == 1
+    _lib.require_cuda(scale, "scale")
+    if abs_max is not None:
+        assert abs_max.dtype == torch.float32 and abs_max.numel() == 1
+        _lib.require_cuda(abs_max, "abs_max")
+    dev = inpt_tensor.device
+    rows, cols = inpt_tensor.shape
+    out = torch.empty_like(inpt_tensor, dtype=fp8_dtype)
+    out_t = torch.empty(cols, rows, dtype=fp8_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call(
+            "tnq_fp8_cast_transpose", inpt_tensor.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_DTYPES[fp8_dtype],
+            scale.data_ptr(), _lib.SCALE_IS_SCALE, int(bool(saturated)), 0 if abs_max is None else abs_max.data_ptr(),
+            out.data_ptr(), out_t.data_ptr(), _lib.workspace(dev).data_ptr() + 4 * _lib.WS_STATUS_WORD,
+            _lib.stream_ptr(dev),
+        )
+    return out, out_t
+
+
+def dynamic_scaled_quant_transpose(inpt_tensor: torch.Tensor, fp8_dtype: torch.dtype = torch.float8_e4m3fn):
+    """Per-tensor dynamic saturated cast of a 2-D bf16 tensor in both layouts:
+    ``(q [R, C], q_t [C, R], scale [1])``.  One amax pass, then one pass that reads the
+    input once and writes both outputs."""
+    _check_matrix(inpt_tensor)
+    _check_fp8(fp8_dtype)
+    dev = inpt_tensor.device
+    rows, cols = inpt_tensor.shape
+    out = torch.empty_like(inpt_tensor, dtype=fp8_dtype)
+    out_t = torch.empty(cols, rows, dtype=fp8_dtype, device=dev)
+    scale = torch.empty(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        ws = _lib.workspace(dev)
+        stream = _lib.stream_ptr(dev)
+        _lib.call("tnq_fp8_amax", inpt_tensor.data_ptr(), inpt_tensor.numel(), _lib.IN_BF16, _lib.FP8_DTYPES[fp8_dtype],
+                  ws.data_ptr(), 0, stream)
+        _lib.call(
+            "tnq_fp8_cast_transpose", inpt_tensor.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_DTYPES[fp8_dtype],
+            ws.data_ptr() + 4 * _lib.WS_SCALE_WORD, _lib.SCALE_IS_SCALE, 1, 0, out.data_ptr(), out_t.data_ptr(),
+            ws.data_ptr() + 4 * _lib.WS_STATUS_WORD, stream,
+        )
+        scale.copy_(ws[_lib.WS_SCALE_WORD:_lib.WS_SCALE_WORD + 1].view(torch.float32))
+    return out, out_t, scale
+
+
 def dynamic_scaled_quant(inpt_tensor: torch.Tensor, fp8_dtype: torch.dtype = torch.float8_e4m3fn) -> torch.Tensor:
     """Quantize to fp8 with the scale computed from the tensor's current amax;
     saturated cast.  Returns the fp8 tensor only, like the reference
