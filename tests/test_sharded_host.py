@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 
 import oracle
 from conftest import as_u8
-from transformer_nuggets_b200.dist.sharded import combine_amax, plan_row_shards
+from transformer_nuggets_b200.dist.sharded import combine_amax, combine_amax_bounded, plan_row_shards
 
 
 @pytest.mark.parametrize("rows,world", [(131072, 8), (131072, 1), (1000, 4), (128, 8), (0, 2), (129, 2)])
@@ -67,3 +67,38 @@ def test_gloo_two_ranks_match_unsharded_oracle():
     results = mp.get_context("spawn").Manager().dict()
     mp.spawn(_entry, args=(world, port, results), nprocs=world, join=True)
     assert dict(results) == {0: 1, 1: 1}
+
+
+def _late_entry(rank, world, port, results):
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # phase 1: the last rank is one second late; the bounded combine still completes
+    amax = torch.tensor([float(rank + 1)])
+    if rank == world - 1:
+        time.sleep(1.0)
+    ok1 = combine_amax_bounded(amax, None, timeout_s=30.0)
+    results[("late", rank)] = (ok1, amax.item())
+    # phase 2: the last rank withholds its contribution; the others give up and report it
+    if rank == world - 1:
+        time.sleep(6.0)
+    else:
+        t0 = time.time()
+        ok2 = combine_amax_bounded(torch.tensor([1.0]), None, timeout_s=2.0)
+        results[("withheld", rank)] = (ok2, time.time() - t0 < 5.5)
+    os._exit(0)  # the group is broken on purpose: leave without a collective shutdown
+
+
+@pytest.mark.timeout(180)
+@pytest.mark.parametrize("world", [2, 3])
+def test_gloo_late_and_withheld_rank(world):
+    port = _free_port()
+    results = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_late_entry, args=(world, port, results), nprocs=world, join=True)
+    got = dict(results)
+    for r in range(world):
+        assert got[("late", r)] == (True, float(world))
+    for r in range(world - 1):
+        assert got[("withheld", r)] == (False, True)

@@ -41,6 +41,25 @@ def combine_amax(local_amax: torch.Tensor, group=None) -> torch.Tensor:
     return local_amax
 
 
+def combine_amax_bounded(local_amax: torch.Tensor, group=None, timeout_s: float = 10.0) -> bool:
+    """``combine_amax`` that gives up: the MAX all-reduce is issued asynchronously and waited
+    for at most ``timeout_s`` seconds.  Returns True when every rank contributed, False when
+    the wait ran out (a rank is late or gone); ``local_amax`` is then not to be trusted and
+    the caller should skip the step or tear the group down.  The host-side counterpart of the
+    bounded device-side wait of the peer exchange."""
+    import datetime
+
+    if local_amax.dtype != torch.float32 or local_amax.numel() != 1:
+        raise TypeError("local_amax must be one fp32 element")
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
+        return True
+    work = dist.all_reduce(local_amax, op=dist.ReduceOp.MAX, group=group, async_op=True)
+    try:
+        return bool(work.wait(datetime.timedelta(seconds=timeout_s)))
+    except RuntimeError:
+        return False
+
+
 def sharded_dynamic_scaled_quant(
     local_rows: torch.Tensor,
     group=None,
