@@ -490,6 +490,8 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_nvfp4(dev, res, timed, report, ws, stream)
     if want("fp8_transpose"):
         _bench_transpose(dev, res, timed, peak, ws, stream)
+    if want("rmsnorm_fp8"):
+        _bench_rmsnorm(dev, res, timed, peak, stream)
     if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
         _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
     st = int(ws[_lib.WS_STATUS_WORD].item())
@@ -538,6 +540,34 @@ def _bench_transpose(dev, res, timed, peak, ws, stream):
     res["fp8_dynamic_cast_transpose"] = report(timed(dynamic, [None]), 6.0,
                                                f"{rows}x{cols}, amax pass + transposing cast, input 256 MiB > L2")
     del x, q, q_t
+
+
+def _bench_rmsnorm(dev, res, timed, peak, stream):
+    """RMSNorm fused into the row-wise e4m3 cast (bf16 16384 x 8192): 2 B read + 1 B written per
+    element; the unfused sequence (norm writes bf16, cast reads it back) moves 7 B per element."""
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
+    x = make_input("fp8_rowwise", dev)
+    rows, cols = x.shape
+    w = torch.ones(cols, dtype=torch.bfloat16, device=dev)
+    q = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    scale = torch.empty(rows, 1, dtype=torch.float32, device=dev)
+
+    def fused(_):
+        _lib.call("tnq_rmsnorm_fp8_rowwise", x.data_ptr(), w.data_ptr(), 1e-6, rows, cols, q.data_ptr(), scale.data_ptr(), 0,
+                  stream)
+
+    ms = timed(fused, [None])
+    gbs = 3.0 * rows * cols / (ms * 1e-3) / 1e9
+    r = {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+         "algorithmic_bytes_per_element": 3.0, "note": f"{rows}x{cols}, norm + per-row scale + cast in one pass, input 256 MiB > L2"}
+    if getattr(timed, "last_distribution", None):
+        r["per_launch_us"] = timed.last_distribution
+    res["rmsnorm_fp8_rowwise"] = r
+    del x, q
 
 
 def _bench_gemv(dev, res, timed, peak, stream, which=None):

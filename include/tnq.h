@@ -117,6 +117,20 @@ int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dty
                            const float* scale, int scale_kind, int saturated, float* abs_max_inout,
                            void* out, void* out_t, uint32_t* status, tnq_stream_t stream);
 
+/* RMSNorm fused into the row-wise dynamic e4m3 cast, bf16 [rows, cols] in, one read:
+ *   y = bf16((f32(x) * rstd) * f32(weight)),  rstd = 1 / sqrt(mean(f32(x)^2) + eps)   per row
+ *   q = e4m3_sat(f32(y) * s),  scale[r] = s = 448 / max(max|y|, 1e-12)                per row
+ * weight is bf16 [cols]; y_bf16 (nullable) also returns the normalised rows.  cols % 16 == 0,
+ * cols <= 16384; x, weight and y_bf16 32-byte aligned, q 16-byte aligned.
+ * The norm is the eager formula the reference profiles for fusion
+ * (`handwritten_rms_norm`, examples/rms_norm_fusion_profile.py:26-31); the cast is
+ * tnq_fp8_rowwise applied to its result.  The mean of squares is summed in a fixed order
+ * (per thread in index order, lanes by butterfly, warps in order): results are run-to-run
+ * identical, and equal to a CPU evaluation except where the other summation order moves a
+ * value across a bf16 rounding boundary. */
+int tnq_rmsnorm_fp8_rowwise(const void* x, const void* weight, float eps, int64_t rows, int64_t cols,
+                            void* q_e4m3, float* scale, void* y_bf16, tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent

@@ -33,6 +33,8 @@ from .cast_oracle import (  # noqa: F401
     nvfp4_dequantize,
     nvfp4_quantize,
     pack_nvfp4_codes,
+    rms_norm,
+    rms_norm_rowwise_quant,
     sharded_fp8_dynamic_quant,
     swizzle_offset,
     to_blocked,

@@ -110,6 +110,29 @@ def fp8_rowwise_quant(a: torch.Tensor, fp8_dtype: torch.dtype):
     return out.to(fp8_dtype), scale
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """Eager RMSNorm: ``(x.float() * rsqrt(mean(x.float()^2, -1) + eps) * weight.float()).to(x.dtype)``.
+
+    Parity: pinned up to summation order - a line-for-line restatement of
+    ``handwritten_rms_norm`` (examples/rms_norm_fusion_profile.py:26-31), checked against
+    the fixture that function wrote.  Every step but ``mean`` is one correctly rounded fp32
+    operation; ``mean`` depends on the order in which the squares are added, so a GPU
+    kernel agrees with this function up to an occasional last-place bf16 rounding."""
+    x32 = x.float()
+    variance = x32.square().mean(dim=-1, keepdim=True)
+    normalized = x32 * torch.rsqrt(variance + eps)
+    return (normalized * weight.float()).to(x.dtype)
+
+
+def rms_norm_rowwise_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, fp8_dtype: torch.dtype = torch.float8_e4m3fn):
+    """RMSNorm followed by the row-wise dynamic cast of its bf16 result:
+    ``(fp8 [M, C], scale [M, 1], y bf16)``.  Restatement (composition of ``rms_norm`` and
+    ``fp8_rowwise_quant``; the reference has no fused op)."""
+    y = rms_norm(x, weight, eps)
+    q, scale = fp8_rowwise_quant(y, fp8_dtype)
+    return q, scale, y
+
+
 def delayed_scale_update(amax_history: torch.Tensor, amax: torch.Tensor, fp8_dtype: torch.dtype):
     """Delayed-scaling state update for a stack of tensors: returns (new history
     [T, L], new scale [T]).  ``history <- roll(history, 1, dim=1); history[:, 0] = amax;

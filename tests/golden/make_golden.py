@@ -14,6 +14,7 @@ fp8 as uint8).  Functions called, by reference path:
 * mx/to_blocked.py:10,75   to_blocked, to_blocked_manual
 * cute/nvfp4_tma.py:941    pack_nvfp4_codes
 * cute/nvfp4_tma.py:946    swizzle_nvfp4_scales
+* examples/rms_norm_fusion_profile.py:26  handwritten_rms_norm  (``--only rmsnorm`` writes just this one)
 """
 
 import os
@@ -37,8 +38,32 @@ def all_bf16_patterns():
     return torch.arange(65536, dtype=torch.int32).to(torch.uint16).view(torch.bfloat16).reshape(256, 256)
 
 
-def main(ref_root):
+def rms_norm_fixture(ref_root):
+    """The eager RMSNorm of the reference's fusion example on seeded bf16 rows (CPU)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("ref_rms_norm_example",
+                                                  os.path.join(ref_root, "examples", "rms_norm_fusion_profile.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    g = torch.Generator().manual_seed(20244)
+    out = {"eps": np.float32(mod.EPS)}
+    for name, (rows, cols) in (("a", (48, 1024)), ("b", (20, 4096)), ("c", (33, 80))):
+        x = (torch.randn(rows, cols, generator=g) * torch.exp2(torch.rand(rows, 1, generator=g) * 12 - 6)).to(torch.bfloat16)
+        w = (1.0 + 0.25 * torch.randn(cols, generator=g)).to(torch.bfloat16)
+        if name == "c":
+            x[5] = 0.0  # an all-zero row: y = 0 * rsqrt(eps) * w = 0
+        y = mod.handwritten_rms_norm(x, w)
+        out[f"x_{name}"], out[f"w_{name}"], out[f"y_{name}"] = bf16_bits(x), bf16_bits(w), bf16_bits(y)
+    np.savez_compressed(os.path.join(HERE, "rms_norm.npz"), **out)
+
+
+def main(ref_root, only=None):
     sys.path.insert(0, ref_root)
+    if only == "rmsnorm":
+        rms_norm_fixture(ref_root)
+        print("rms_norm.npz written to", HERE)
+        return
     from transformer_nuggets.cute.mxfp8_tma import quantize_mxfp8_tensor
     from transformer_nuggets.cute.nvfp4_tma import pack_nvfp4_codes, swizzle_nvfp4_scales
     from transformer_nuggets.fp8.scaled_quant import eager_scaled_quant
@@ -141,8 +166,11 @@ def main(ref_root):
         os.path.join(HERE, "nvfp4_format.npz"),
         codes=codes.numpy(), packed=packed.numpy(), scales=scales.numpy(), swizzled=sw.numpy(),
     )
+    rms_norm_fixture(ref_root)
     print("golden fixtures written to", HERE)
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    only = "rmsnorm" if "--only" in sys.argv and "rmsnorm" in sys.argv else None
+    main(args[0] if args and args[0] != "rmsnorm" else "/root/reference", only)

@@ -148,3 +148,19 @@ def test_sharded_equals_unsharded():
         parts, s2 = oracle.sharded_fp8_dynamic_quant(list(x.chunk(n)), torch.float8_e4m3fn)
         assert torch.equal(s, s2)
         assert torch.equal(as_u8(torch.cat(parts)), as_u8(full))
+
+
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_rms_norm_matches_reference_fixture(golden, name):
+    """oracle.rms_norm against the rows the reference's eager RMSNorm produced
+    (examples/rms_norm_fusion_profile.py:26-31).  The same formula on the same CPU build is
+    identical; another vector width may add the squares in another order, hence the
+    last-place allowance."""
+    z = golden("rms_norm.npz")
+    x, w, y = (bf16_from_bits(z[f"{k}_{name}"]) for k in ("x", "w", "y"))
+    got = oracle.rms_norm(x, w, float(z["eps"]))
+    ia, ib = got.view(torch.int16).to(torch.int32), y.view(torch.int16).to(torch.int32)
+    assert (ia - ib).abs().max().item() <= 1
+    assert (ia != ib).float().mean().item() <= 5e-3
+    q, scale, y2 = oracle.rms_norm_rowwise_quant(x, w, float(z["eps"]))
+    assert torch.equal(y2.view(torch.int16), got.view(torch.int16)) and scale.shape == (x.shape[0], 1)

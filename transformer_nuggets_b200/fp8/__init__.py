@@ -7,3 +7,4 @@ from .scaled_quant import (  # noqa: F401
     scaled_quant_transpose,
 )
 from .delayed_scaling import DelayedScaling, combine_amaxes  # noqa: F401
+from .rms_norm_quant import rms_norm_rowwise_quant  # noqa: F401
