@@ -13,6 +13,9 @@
 namespace tnq {
 
 constexpr int kRowThreads = 256;
+#ifndef TNQ_ROW_PREFETCH
+#define TNQ_ROW_PREFETCH 1
+#endif
 
 template <int IN>
 struct RowIn;
@@ -83,22 +86,31 @@ __global__ void __launch_bounds__(kRowThreads)
   const int64_t row_bytes = (int64_t)nvec_row * 32;
   const int64_t n_steps = (rows + kGroups - 1) / kGroups;  // identical trip count for every thread of a CTA
 
-  for (int64_t step = blockIdx.x; step < n_steps; step += gridDim.x) {
+  // Where the registers allow (bf16, VPT <= 2) the next row's loads are issued before this row's
+  // reduction and cast, so a CTA always has two rows of reads in flight.
+  constexpr bool kPrefetch = TNQ_ROW_PREFETCH && VPT <= 2;
+  auto load_row = [&](Vec32B (&dst)[VPT], int64_t step) {
     const int64_t r = step * kGroups + g;
-    const bool live = r < rows;
+    const bool ok = step < n_steps && r < rows;
     const uint8_t* xr = x + r * row_bytes;
-    Vec32B v[VPT];
-    uint32_t m = 0;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int vi = t + k * G;
-      if (live && vi < nvec_row) {
-        v[k] = ldg256(xr + (int64_t)vi * 32);
+      if (ok && vi < nvec_row) {
+        dst[k] = ldg256(xr + (int64_t)vi * 32);
       } else {
 #pragma unroll
-        for (int w = 0; w < 8; ++w) v[k].w[w] = 0u;
+        for (int w = 0; w < 8; ++w) dst[k].w[w] = 0u;
       }
     }
+  };
+  Vec32B v[VPT], vn[kPrefetch ? VPT : 1];
+  load_row(v, blockIdx.x);
+  for (int64_t step = blockIdx.x; step < n_steps; step += gridDim.x) {
+    const int64_t r = step * kGroups + g;
+    const bool live = r < rows;
+    if constexpr (kPrefetch) load_row(vn, step + gridDim.x);
+    uint32_t m = 0;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) m = T::absmax(m, v[k]);
     m = T::fold(m);
@@ -115,7 +127,8 @@ __global__ void __launch_bounds__(kRowThreads)
       for (int w = 0; w < kWarpsPerGroup; ++w) mm = max(mm, s_part[g * kWarpsPerGroup + w]);
       m = mm;
     }
-    if (!live) continue;
+    do {
+    if (!live) break;
     const float amax = __uint_as_float(m);
     const bool finite = m < 0x7f800000u;  // uniform over the row's threads
     if constexpr (IN == TNQ_IN_BF16) {
@@ -127,7 +140,7 @@ __global__ void __launch_bounds__(kRowThreads)
 #pragma unroll
         for (int k = 0; k < VPT; ++k)
           if (t + k * G < nvec_row) row_quant_store_both_bf16(v[k], sa, sb, qa, qb, t + k * G);
-        continue;
+        break;
       }
     }
     if (q43) {
@@ -157,6 +170,13 @@ __global__ void __launch_bounds__(kRowThreads)
         for (int k = 0; k < VPT; ++k)
           if (t + k * G < nvec_row) row_quant_store<IN, TNQ_FP8_E5M2, false>(v[k], s, qr, t + k * G);
       }
+    }
+    } while (false);
+    if constexpr (kPrefetch) {
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) v[k] = vn[k];
+    } else {
+      load_row(v, step + gridDim.x);
     }
   }
 }
