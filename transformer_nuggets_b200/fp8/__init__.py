@@ -1,5 +1,7 @@
 from .scaled_quant import (  # noqa: F401
     dynamic_scaled_quant,
+    eager_dynamic_scaled_quant,
+    eager_scaled_quant,
     dynamic_scaled_quant_transpose,
     dynamic_scaled_quant_with_scale,
     rowwise_scaled_quant,

@@ -85,6 +85,26 @@ def dynamic_scaled_quant_with_scale(
     return out, scale
 
 
+def eager_scaled_quant(
+    a: torch.Tensor,
+    scale: torch.Tensor,
+    abs_max: torch.Tensor,
+    fp8_dtype: torch.dtype,
+    saturated: bool = False,
+) -> torch.Tensor:
+    """The reference's ``eager_scaled_quant`` (fp8/scaled_quant.py:78-102) under its own name,
+    served by the same CUDA kernel as ``scaled_quant``: identical bytes, and ``abs_max`` is
+    OVERWRITTEN with ``max|a|`` (the eager twin fills, the fused kernel accumulates)."""
+    abs_max.zero_()
+    return scaled_quant(a, scale, abs_max, fp8_dtype, saturated)
+
+
+def eager_dynamic_scaled_quant(a: torch.Tensor, fp8_dtype: torch.dtype) -> torch.Tensor:
+    """The reference's ``eager_dynamic_scaled_quant`` (fp8/scaled_quant.py:172-186) under its own
+    name: ``scale = finfo.max / max(amax, 1e-12)``, saturated cast, served by the CUDA path."""
+    return dynamic_scaled_quant(a, fp8_dtype)
+
+
 def _check_matrix(inpt_tensor: torch.Tensor):
     _check_input(inpt_tensor)
     if inpt_tensor.dim() != 2:
