@@ -567,6 +567,21 @@ def _bench_rmsnorm(dev, res, timed, peak, stream):
     if getattr(timed, "last_distribution", None):
         r["per_launch_us"] = timed.last_distribution
     res["rmsnorm_fp8_rowwise"] = r
+
+    sf = torch.empty(512 * (rows // 128) * (cols // 128), dtype=torch.uint8, device=dev)  # swizzled, no padding here
+
+    def fused_mx(_):
+        _lib.call("tnq_rmsnorm_mxfp8", x.data_ptr(), w.data_ptr(), 1e-6, rows, cols, q.data_ptr(), sf.data_ptr(),
+                  _lib.E8M0_CEIL, _lib.SCALES_SWIZZLED, 0, stream)
+
+    ms = timed(fused_mx, [None])
+    bpe = 3.0 + 1.0 / 32
+    gbs = bpe * rows * cols / (ms * 1e-3) / 1e9
+    r = {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+         "algorithmic_bytes_per_element": bpe, "note": f"{rows}x{cols}, norm + MXFP8 row-wise quantize, swizzled scales"}
+    if getattr(timed, "last_distribution", None):
+        r["per_launch_us"] = timed.last_distribution
+    res["rmsnorm_mxfp8"] = r
     del x, q
 
 

@@ -131,6 +131,25 @@ int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dty
 int tnq_rmsnorm_fp8_rowwise(const void* x, const void* weight, float eps, int64_t rows, int64_t cols,
                             void* q_e4m3, float* scale, void* y_bf16, tnq_stream_t stream);
 
+/* The same fused RMSNorm with the MXFP8 row-wise quantizer behind it: q = e4m3(y * 2^-e) per
+ * 32-element block along the row, E8M0 byte e + 127 into sf (raw [rows, cols / 32] or swizzled
+ * 128x4; a swizzled buffer must be zero-filled by the caller where rows % 128 or
+ * (cols / 32) % 4 leave padding), exponent rule as tnq_mxfp8_quantize.  cols % 32 == 0,
+ * cols <= 16384.  Norm: examples/rms_norm_fusion_profile.py:26-31; quantizer:
+ * `quantize_mxfp8_tensor`, cute/mxfp8_tma.py:497-504. */
+int tnq_rmsnorm_mxfp8(const void* x, const void* weight, float eps, int64_t rows, int64_t cols, void* q_e4m3,
+                      void* sf, int scale_mode, int scale_layout, void* y_bf16, tnq_stream_t stream);
+
+/* SwiGLU fused into the same two quantizers: y = bf16(f32(bf16(silu(f32(a)))) * f32(b)) with
+ * silu(a) = a / (1 + exp(-a)), a and b bf16 [rows, cols] - the eager bf16 evaluation of
+ * `F.silu(self.w1(x)) * self.w3(x)` (llama/model.py:228), the operand of the next GEMM - then
+ * the row-wise dynamic e4m3 cast / the MXFP8 row-wise quantizer on y.  Shapes, alignment and
+ * the optional y_bf16 as for the RMSNorm entry points. */
+int tnq_swiglu_fp8_rowwise(const void* a, const void* b, int64_t rows, int64_t cols, void* q_e4m3, float* scale,
+                           void* y_bf16, tnq_stream_t stream);
+int tnq_swiglu_mxfp8(const void* a, const void* b, int64_t rows, int64_t cols, void* q_e4m3, void* sf,
+                     int scale_mode, int scale_layout, void* y_bf16, tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent

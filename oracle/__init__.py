@@ -36,6 +36,7 @@ from .cast_oracle import (  # noqa: F401
     rms_norm,
     rms_norm_rowwise_quant,
     sharded_fp8_dynamic_quant,
+    swiglu,
     swizzle_offset,
     to_blocked,
     to_blocked_closed_form,

@@ -133,6 +133,14 @@ def rms_norm_rowwise_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, fp
     return q, scale, y
 
 
+def swiglu(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``F.silu(a) * b`` on bf16 tensors, evaluated eagerly: the operand of ``w2`` in the
+    reference's ``FeedForward`` (llama/model.py:228).  Parity: restatement of that expression
+    (the same two torch ops); ``exp`` is not correctly rounded, so a GPU evaluation agrees up
+    to an occasional last-place bf16 rounding."""
+    return torch.nn.functional.silu(a) * b
+
+
 def delayed_scale_update(amax_history: torch.Tensor, amax: torch.Tensor, fp8_dtype: torch.dtype):
     """Delayed-scaling state update for a stack of tensors: returns (new history
     [T, L], new scale [T]).  ``history <- roll(history, 1, dim=1); history[:, 0] = amax;

@@ -11,7 +11,8 @@ import torch
 
 import oracle
 from conftest import as_u8, bf16_from_bits
-from transformer_nuggets_b200.fp8 import rms_norm_rowwise_quant
+from transformer_nuggets_b200.fp8 import (rms_norm_quantize_mxfp8, rms_norm_rowwise_quant, swiglu_quantize_mxfp8,
+                                          swiglu_rowwise_quant)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -99,3 +100,79 @@ def test_argument_checks():
                                torch.ones(32768, dtype=torch.bfloat16, device=DEV))
     q, s = rms_norm_rowwise_quant(torch.zeros(0, 64, dtype=torch.bfloat16, device=DEV), w)
     assert q.shape == (0, 64) and s.shape == (0, 1)
+
+
+@pytest.mark.parametrize("shape", [(1, 32), (7, 64), (130, 1056), (256, 4096), (128, 8192), (9, 16384), (2, 5, 2048)])
+@pytest.mark.parametrize("mode", ["ceil", "floor"])
+def test_fused_mxfp8(shape, mode):
+    """Stage 1 as above; stage 2: payload and E8M0 bytes bit-exact against the oracle's MXFP8
+    quantizer applied to the normalised rows the kernel used; swizzled == to_blocked(raw)."""
+    g = torch.Generator().manual_seed(sum(shape) + len(mode))
+    x = (torch.randn(*shape, generator=g) * torch.exp2(torch.rand(*shape[:-1], 1, generator=g) * 10 - 5)).to(torch.bfloat16)
+    w = (1.0 + 0.3 * torch.randn(shape[-1], generator=g)).to(torch.bfloat16)
+    q, sf, y = rms_norm_quantize_mxfp8(x.to(DEV), w.to(DEV), 1e-5, scale_mode=mode, return_normed=True)
+    y_cpu = y.cpu()
+    d = _ulp_distance(y_cpu, oracle.rms_norm(x, w, 1e-5))
+    assert d.max().item() <= 1 and (d != 0).float().mean().item() <= 5e-3
+    y2 = y_cpu.reshape(-1, shape[-1])
+    want_q, want_sf = oracle.mxfp8_quantize(y2, mode)
+    assert torch.equal(as_u8(q).cpu().reshape(want_q.shape), as_u8(want_q))
+    assert torch.equal(sf.cpu(), want_sf)
+    q2, sf2 = rms_norm_quantize_mxfp8(x.to(DEV), w.to(DEV), 1e-5, scale_mode=mode, swizzle=True)
+    assert torch.equal(as_u8(q2), as_u8(q)) and torch.equal(sf2.cpu(), oracle.to_blocked(want_sf))
+
+
+def test_fused_mxfp8_argument_checks():
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.ones(64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        rms_norm_quantize_mxfp8(x[:, :48].contiguous(), w[:48].contiguous())  # 48 is not a multiple of 32
+    with pytest.raises(ValueError):
+        rms_norm_quantize_mxfp8(x, w, scale_mode="nearest")
+    with pytest.raises(TypeError):
+        rms_norm_quantize_mxfp8(x.float(), w)
+
+
+def _swiglu_inputs(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = (torch.randn(*shape, generator=g) * 3.0).to(torch.bfloat16)
+    b = (torch.randn(*shape, generator=g) * torch.exp2(torch.rand(*shape[:-1], 1, generator=g) * 8 - 4)).to(torch.bfloat16)
+    return a, b
+
+
+@pytest.mark.parametrize("shape", [(1, 16), (9, 48), (130, 1040), (256, 4096), (64, 8192), (5, 14336), (2, 3, 2048)])
+def test_swiglu_rowwise(shape):
+    a, b = _swiglu_inputs(shape, sum(shape))
+    q, scale, y = swiglu_rowwise_quant(a.to(DEV), b.to(DEV), return_activation=True)
+    y_cpu = y.cpu()
+    d = _ulp_distance(y_cpu, oracle.swiglu(a, b))
+    assert d.max().item() <= 1 and (d != 0).float().mean().item() <= 2e-2
+    want_q, want_scale = oracle.fp8_rowwise_quant(y_cpu.reshape(-1, shape[-1]), torch.float8_e4m3fn)
+    assert torch.equal(as_u8(q).cpu().reshape(want_q.shape), as_u8(want_q))
+    assert torch.equal(scale.cpu().reshape(-1, 1).view(torch.int32), want_scale.view(torch.int32))
+    q2, scale2 = swiglu_rowwise_quant(a.to(DEV), b.to(DEV))
+    assert torch.equal(as_u8(q2), as_u8(q)) and torch.equal(scale2, scale)
+
+
+@pytest.mark.parametrize("shape", [(3, 32), (130, 1056), (256, 4096), (33, 8192), (4, 14336)])
+@pytest.mark.parametrize("mode", ["ceil", "floor"])
+def test_swiglu_mxfp8(shape, mode):
+    a, b = _swiglu_inputs(shape, sum(shape) + 1)
+    q, sf, y = swiglu_quantize_mxfp8(a.to(DEV), b.to(DEV), scale_mode=mode, return_activation=True)
+    y_cpu = y.cpu()
+    d = _ulp_distance(y_cpu, oracle.swiglu(a, b))
+    assert d.max().item() <= 1 and (d != 0).float().mean().item() <= 2e-2
+    want_q, want_sf = oracle.mxfp8_quantize(y_cpu.reshape(-1, shape[-1]), mode)
+    assert torch.equal(as_u8(q).cpu().reshape(want_q.shape), as_u8(want_q)) and torch.equal(sf.cpu(), want_sf)
+    q2, sf2 = swiglu_quantize_mxfp8(a.to(DEV), b.to(DEV), scale_mode=mode, swizzle=True)
+    assert torch.equal(as_u8(q2), as_u8(q)) and torch.equal(sf2.cpu(), oracle.to_blocked(want_sf))
+
+
+def test_swiglu_argument_checks():
+    a = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        swiglu_rowwise_quant(a, a[:, :32].contiguous())
+    with pytest.raises(TypeError):
+        swiglu_rowwise_quant(a.float(), a.float())
+    with pytest.raises(ValueError):
+        swiglu_quantize_mxfp8(a[:, :48].contiguous(), a[:, :48].contiguous())

@@ -21,8 +21,8 @@ CSRC = os.path.join(PKG, "csrc")
 OBJ_DIR = os.path.join(ROOT, "build", "tnq")
 LIB_PATH = os.path.join(CSRC, "libtnq.so")
 
-SOURCES = ["fp8_tensor.cu", "fp8_fused.cu", "fp8_rowwise.cu", "mxfp8.cu", "nvfp4.cu", "to_blocked.cu", "exchange.cu", "gemv.cu", "delayed.cu", "fp8_transpose.cu", "rmsnorm_fp8.cu"]
-HEADERS = ["common.cuh", "tile_pipeline.cuh", os.path.join(ROOT, "include", "tnq.h")]
+SOURCES = ["fp8_tensor.cu", "fp8_fused.cu", "fp8_rowwise.cu", "mxfp8.cu", "nvfp4.cu", "to_blocked.cu", "exchange.cu", "gemv.cu", "delayed.cu", "fp8_transpose.cu", "producer_quant.cu"]
+HEADERS = ["common.cuh", "tile_pipeline.cuh", "mx_scale.cuh", os.path.join(ROOT, "include", "tnq.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

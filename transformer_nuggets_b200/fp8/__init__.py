@@ -9,4 +9,9 @@ from .scaled_quant import (  # noqa: F401
     scaled_quant_transpose,
 )
 from .delayed_scaling import DelayedScaling, combine_amaxes  # noqa: F401
-from .rms_norm_quant import rms_norm_rowwise_quant  # noqa: F401
+from .rms_norm_quant import (  # noqa: F401
+    rms_norm_quantize_mxfp8,
+    rms_norm_rowwise_quant,
+    swiglu_quantize_mxfp8,
+    swiglu_rowwise_quant,
+)
