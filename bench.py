@@ -582,7 +582,22 @@ def _bench_rmsnorm(dev, res, timed, peak, stream):
     if getattr(timed, "last_distribution", None):
         r["per_launch_us"] = timed.last_distribution
     res["rmsnorm_mxfp8"] = r
-    del x, q
+
+    # SwiGLU producer: two bf16 inputs (4 B read), one fp8 output (1 B written) per element
+    b = make_input("fp8_rowwise", dev)
+
+    def fused_swiglu(_):
+        _lib.call("tnq_swiglu_fp8_rowwise", x.data_ptr(), b.data_ptr(), rows, cols, q.data_ptr(), scale.data_ptr(), 0, stream)
+
+    ms = timed(fused_swiglu, [None])
+    gbs = 5.0 * rows * cols / (ms * 1e-3) / 1e9
+    r = {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+         "algorithmic_bytes_per_element": 5.0,
+         "note": f"{rows}x{cols}, silu(a) * b + per-row scale + cast in one pass (unfused: 11 B/elem)"}
+    if getattr(timed, "last_distribution", None):
+        r["per_launch_us"] = timed.last_distribution
+    res["swiglu_fp8_rowwise"] = r
+    del x, q, b
 
 
 def _bench_gemv(dev, res, timed, peak, stream, which=None):

@@ -23,8 +23,9 @@
 //
 // SwiGLU: y = bf16( f32(bf16(silu(f32(a)))) * f32(b) ), silu(a) = a / (1 + exp(-a)) - the eager
 // bf16 evaluation of `F.silu(w1(x)) * w3(x)` (llama/model.py:228), whose result is the operand
-// of the next GEMM.  expf is not correctly rounded, so here too y can differ from a CPU run in
-// an occasional last-place bf16 rounding while the quantization of y is exact.
+// of the next GEMM.  exp and the division use the hardware approximations (ex2.approx, rcp:
+// relative error near 2^-21), so here too y can differ from a CPU run in an occasional
+// last-place bf16 rounding while the quantization of y is exact.
 //
 // A row is owned by G threads holding their share (VPT 32-byte vectors each) in registers; where
 // the registers allow (VPT <= 2) the next row's loads are issued before this row's arithmetic.
@@ -74,7 +75,8 @@ __device__ __forceinline__ uint32_t swiglu_pk(uint32_t a_pk, uint32_t b_pk) {
   float a0, a1, b0, b1;
   widen_pk(a_pk, a0, a1);
   widen_pk(b_pk, b0, b1);
-  const float s0 = __fdiv_rn(a0, __fadd_rn(1.0f, expf(-a0))), s1 = __fdiv_rn(a1, __fadd_rn(1.0f, expf(-a1)));
+  // ex2.approx and the approximate division: relative error near 2^-21, far below half a bf16 step
+  const float s0 = __fdividef(a0, __fadd_rn(1.0f, __expf(-a0))), s1 = __fdividef(a1, __fadd_rn(1.0f, __expf(-a1)));
   uint32_t s_pk;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(s_pk) : "f"(s1), "f"(s0));
   float t0, t1;
