@@ -9,7 +9,7 @@ from .scaled_quant import (  # noqa: F401
     scaled_quant_transpose,
 )
 from .delayed_scaling import DelayedScaling, combine_amaxes  # noqa: F401
-from .rms_norm_quant import (  # noqa: F401
+from .producer_quant import (  # noqa: F401
     rms_norm_quantize_mxfp8,
     rms_norm_rowwise_quant,
     swiglu_quantize_mxfp8,
