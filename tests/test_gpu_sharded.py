@@ -107,6 +107,21 @@ def _nccl_rank(rank, world, port, results):
             if exchange is not None:
                 ok = ok and exchange.status() == 0
                 exchange.close()
+        # delayed scaling, data parallel: every rank casts its rows with the shared scale, sync()
+        # MAX-reduces the amax words over the group, so all ranks derive the same next scale
+        from transformer_nuggets_b200.fp8 import DelayedScaling
+
+        state = DelayedScaling(1, history_len=4, device=torch.device("cuda", rank))
+        o_hist, o_scale = torch.zeros(1, 4), torch.ones(1)
+        for step in range(3):
+            xs = (x * (0.5 + step)).to(torch.bfloat16)
+            q = state.cast(0, xs[s:e].cuda(), saturated=True)
+            am = torch.zeros(1)
+            want_q = oracle.fp8_scaled_quant(xs, o_scale.clone(), am, torch.float8_e4m3fn, True)
+            ok = ok and torch.equal(as_u8(q).cpu(), as_u8(want_q[s:e]))
+            state.sync(None)
+            o_hist, o_scale = oracle.delayed_scale_update(o_hist, am, torch.float8_e4m3fn)
+            ok = ok and torch.equal(state.scale.cpu(), o_scale) and torch.equal(state.amax_history.cpu(), o_hist)
         results[rank] = 1 if ok else 0
     finally:
         dist.destroy_process_group()
