@@ -492,6 +492,8 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_transpose(dev, res, timed, peak, ws, stream)
     if want("rmsnorm_fp8"):
         _bench_rmsnorm(dev, res, timed, peak, stream)
+    if only == "fp8_gemm":  # tensor-core row; not part of the default run (a seconds-long dense GEMM loop)
+        _bench_fp8_gemm(dev, res, timed, stream)
     if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
         _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
     st = int(ws[_lib.WS_STATUS_WORD].item())
@@ -598,6 +600,50 @@ def _bench_rmsnorm(dev, res, timed, peak, stream):
         r["per_launch_us"] = timed.last_distribution
     res["swiglu_fp8_rowwise"] = r
     del x, q, b
+
+
+def _bench_fp8_gemm(dev, res, timed, stream):
+    """e4m3 GEMM with per-tensor scale epilogue, M = N = K = 8192 (tensor-core bound: 2*M*N*K flops),
+    with the library GEMM (torch._scaled_mm, cuBLASLt) timed beside it on the same operands."""
+    import json
+
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+
+    m = n = k = 8192
+    g = torch.Generator(device=dev).manual_seed(4001)
+    a = torch.randn(m, k, device=dev, generator=g).to(torch.float8_e4m3fn)
+    b_nk = torch.randn(n, k, device=dev, generator=g).to(torch.float8_e4m3fn)
+    sa = torch.full((1,), 0.5, dtype=torch.float32, device=dev)
+    sb = torch.full((1,), 0.25, dtype=torch.float32, device=dev)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    status = _lib.workspace(dev).data_ptr() + 4 * _lib.WS_STATUS_WORD
+
+    def ours(_):
+        _lib.call("tnq_fp8_gemm", a.data_ptr(), b_nk.data_ptr(), sa.data_ptr(), sb.data_ptr(), 0, _lib.FP8_E4M3, m, n, k,
+                  c.data_ptr(), status, stream)
+
+    def library(_):
+        torch._scaled_mm(a, b_nk.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+
+    flops = 2.0 * m * n * k
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
+    ms = timed(ours, [None])
+    ms_lib = timed(library, [None])
+    res["fp8_gemm"] = {
+        "us": ms * 1e3, "TFLOPs": flops / (ms * 1e-3) / 1e12, "library_us": ms_lib * 1e3,
+        "library_TFLOPs": flops / (ms_lib * 1e-3) / 1e12, "frac_of_library": ms_lib / ms,
+        "frac_of_measured_bf16_peak": flops / (ms * 1e-3) / 1e12 / bf16_peak,
+        "note": f"e4m3 {m}x{n}x{k}, per-tensor scales, bf16 out; measured dense bf16 peak {bf16_peak} TF/s "
+                "(fp8 nominal is twice the bf16 figure)",
+    }
 
 
 def _bench_gemv(dev, res, timed, peak, stream, which=None):

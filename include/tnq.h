@@ -150,6 +150,18 @@ int tnq_swiglu_fp8_rowwise(const void* a, const void* b, int64_t rows, int64_t c
 int tnq_swiglu_mxfp8(const void* a, const void* b, int64_t rows, int64_t cols, void* q_e4m3, void* sf,
                      int scale_mode, int scale_layout, void* y_bf16, tnq_stream_t stream);
 
+/* FP8 GEMM with a scale epilogue on the tensor cores (tcgen05, accumulator in tensor memory):
+ *   out[m, n] = bf16( (sum_k a[m, k] * b[n, k]) * a_scale[rowwise ? m : 0] * b_scale[rowwise ? n : 0] )
+ * a [M, K] and b [N, K] hold fp8 bytes of `fp8_dtype` with K contiguous (row-major activation,
+ * "column-major" weight); scales are fp32 in the DEQUANTISATION direction (the reciprocal of what
+ * the casts return), one element each or a_scale [M], b_scale [N].  K % 16 == 0; a, b, out
+ * 16-byte aligned.  `status` (nullable) receives TNQ_ETIMEOUT if a bounded wait gives up.
+ * Replaces `matmul_kernel_persistent` / `matmul_kernel_tma_persistent` and their launchers with
+ * `apply_scaling` (fp8/fp8_matmul.py:97-138, 142-288, 290-474). */
+int tnq_fp8_gemm(const void* a, const void* b, const float* a_scale, const float* b_scale, int rowwise,
+                 int fp8_dtype, int64_t m, int64_t n, int64_t k, void* out_bf16, uint32_t* status,
+                 tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent

@@ -24,6 +24,7 @@ from .cast_oracle import (  # noqa: F401
     e8m0_exponent_ceil_int,
     e8m0_exponent_floor_int,
     fp8_dynamic_quant,
+    fp8_matmul,
     fp8_rowwise_quant,
     fp8_scaled_quant,
     mxfp8_dequantize,

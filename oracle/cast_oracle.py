@@ -141,6 +141,16 @@ def swiglu(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.silu(a) * b
 
 
+def fp8_matmul(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor) -> torch.Tensor:
+    """``bf16((a.float() @ b.float()) * (a_scale * b_scale))`` with ``a [M, K]``, ``b [K, N]`` fp8 and
+    per-tensor (one element) or row-wise (``[M, 1]``, ``[1, N]``) fp32 scales: the arithmetic of
+    ``apply_scaling`` behind the reference's matmul kernels (fp8/fp8_matmul.py:109-138, 215-238).
+    Floating point: products of two fp8 values are exact in fp32, the order of the fp32
+    accumulation is not fixed, so comparisons use a tolerance."""
+    acc = a.float() @ b.float()
+    return (acc * (a_scale.float() * b_scale.float())).to(torch.bfloat16)
+
+
 def delayed_scale_update(amax_history: torch.Tensor, amax: torch.Tensor, fp8_dtype: torch.dtype):
     """Delayed-scaling state update for a stack of tensors: returns (new history
     [T, L], new scale [T]).  ``history <- roll(history, 1, dim=1); history[:, 0] = amax;

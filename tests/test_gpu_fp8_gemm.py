@@ -1,0 +1,65 @@
+"""FP8 GEMM with scale epilogue (tcgen05) against the oracle's fp32 matmul of the same fp8
+operands and against the library GEMM (torch._scaled_mm).  Floating point: products are exact,
+the accumulation order differs, the result is rounded to bf16 - compared within one bf16 step
+of relative error."""
+
+import pytest
+import torch
+
+import oracle
+from transformer_nuggets_b200 import _lib
+from transformer_nuggets_b200.fp8.fp8_matmul import matmul_persistent, matmul_tma_persistent
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _operands(m, n, k, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = (torch.randn(m, k, generator=g) * 2.0).to(dtype)
+    b_nk = (torch.randn(n, k, generator=g) * 2.0).to(dtype)  # weight stored [N, K]
+    return a, b_nk
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (100, 72, 80), (2, 8, 16),
+                                   (300, 520, 272), (1024, 1024, 4096)])
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("row_wise", [False, True])
+def test_matches_oracle(m, n, k, dtype, row_wise):
+    a, b_nk = _operands(m, n, k, dtype, m + n + k)
+    g = torch.Generator().manual_seed(7)
+    if row_wise:
+        a_scale = torch.rand(m, 1, generator=g) + 0.5
+        b_scale = torch.rand(1, n, generator=g) + 0.5
+    else:
+        a_scale, b_scale = torch.tensor([0.75]), torch.tensor([1.5])
+    want = oracle.fp8_matmul(a, a_scale, b_nk.t(), b_scale)
+    got = matmul_persistent(a.to(DEV), a_scale.to(DEV), b_nk.to(DEV).t(), b_scale.to(DEV), torch.bfloat16)
+    st = int(_lib.workspace(torch.device(DEV, 0))[_lib.WS_STATUS_WORD].item())
+    assert st == 0
+    assert got.shape == (m, n) and got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2 ** -7, atol=2 ** -7 * float(k) ** 0.5)
+
+
+def test_against_library_gemm():
+    m, n, k = 2048, 4096, 4096
+    a, b_nk = _operands(m, n, k, torch.float8_e4m3fn, 3)
+    a, b_nk = a.to(DEV), b_nk.to(DEV)
+    sa, sb = torch.tensor([0.5], device=DEV), torch.tensor([0.25], device=DEV)
+    got = matmul_tma_persistent(a, sa, b_nk.t(), sb, torch.bfloat16)
+    ref = torch._scaled_mm(a, b_nk.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+    torch.testing.assert_close(got.float(), ref.float(), rtol=2 ** -7, atol=1.0)
+
+
+def test_argument_checks():
+    a = torch.zeros(16, 32, device=DEV).to(torch.float8_e4m3fn)
+    b = torch.zeros(8, 32, device=DEV).to(torch.float8_e4m3fn)
+    one = torch.ones(1, device=DEV)
+    with pytest.raises(AssertionError):
+        matmul_persistent(a, one, b, one)  # b is [N, K], not [K, N]
+    with pytest.raises(ValueError):
+        matmul_persistent(a, one, b.t().contiguous(), one)  # b row-major
+    with pytest.raises(AssertionError):
+        matmul_persistent(a, torch.ones(16, 1, device=DEV), b.t(), torch.ones(1, 5, device=DEV))
+    with pytest.raises(TypeError):
+        matmul_persistent(a, one, b.t(), one, torch.float16)
