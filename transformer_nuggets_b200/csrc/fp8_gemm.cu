@@ -4,13 +4,15 @@
 // library produce for an activation and for a weight.  The consumer of the per-tensor and
 // row-wise casts.
 //
-// One CTA computes a 128 x 256 tile of C.  Warp 0 (one elected lane) streams 128 x 128-byte
+// A CTA computes 128 x 256 tiles of C, one after another (persistent grid, one CTA per SM, grouped
+// tile order for L2 reuse).  Warp 0 (one elected lane) streams 128 x 128-byte
 // tiles of A and 256 x 128-byte tiles of B into a ring of shared-memory stages with 2-D TMA
 // loads (128-byte swizzle, one mbarrier per stage).  Warp 1 (one elected lane) issues
 // tcgen05.mma (kind::f8f6f4, M = 128, N = 256, K = 32 per instruction, four per stage) with
 // both operands read from shared memory through matrix descriptors and the fp32 accumulator
-// in tensor memory (256 of the SM's 512 columns); tcgen05.commit hands a finished stage back
-// to the loader and, after the last one, the accumulator to the epilogue.  Warps 2-5 (one
+// in tensor memory (two accumulators of 256 columns: the epilogue of one tile overlaps the MMAs of
+// the next); tcgen05.commit hands a finished stage back to the loader and, after a tile's last
+// one, the accumulator to the epilogue.  Warps 2-5 (one
 // per 32-lane quarter of tensor memory) read the accumulator with tcgen05.ld, apply the
 // scales, round to bf16 and store rows.  Every wait is bounded (about one second): on expiry
 // the CTA records TNQ_ETIMEOUT, the roles fall through to the common exit and the tensor
@@ -26,7 +28,7 @@ constexpr int kGemmStages = 4;
 constexpr int kGemmATile = kGemmBM * kGemmBK, kGemmBTile = kGemmBN * kGemmBK;
 constexpr int kGemmStageBytes = kGemmATile + kGemmBTile;
 constexpr int kGemmThreads = 192;
-constexpr int kGemmTmemCols = 256;
+constexpr int kGemmTmemCols = 512;  // two 128 x 256 fp32 accumulators
 constexpr int kGemmSmemBytes = kGemmStages * kGemmStageBytes + 1024 /* alignment */ + 128 /* barriers */;
 
 // shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
@@ -69,6 +71,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
+// Tile t of the (tiles_m x tiles_n) grid in a grouped order: kGemmGroupM consecutive row-tiles are
+// swept across all column-tiles before the next group starts, so the tiles in flight at one
+// time share a small set of A and B panels in L2.
+constexpr int kGemmGroupM = 8;
+__device__ __forceinline__ void gemm_tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = kGemmGroupM * tiles_n;
+  const int group = t / per_group, in_group = t % per_group;
+  const int first_m = group * kGemmGroupM;
+  const int rows_here = min(kGemmGroupM, tiles_m - first_m);
+  tm = first_m + in_group % rows_here;
+  tn = in_group / rows_here;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: CTA c computes tiles c, c + gridDim.x, ...  The accumulator is double-buffered in
+// tensor memory (2 x 256 columns) so that the epilogue of one tile overlaps the MMAs of the next.
 __global__ void __launch_bounds__(kGemmThreads, 1)
     k_fp8_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const float* __restrict__ a_scale, const float* __restrict__ b_scale, int rowwise, int fmt, int m, int n,
@@ -77,19 +97,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint8_t* const base = tnq_gemm_smem + ((1024u - (smem_u32(tnq_gemm_smem) & 1023u)) & 1023u);
   uint64_t* const full = reinterpret_cast<uint64_t*>(base + kGemmStages * kGemmStageBytes);
   uint64_t* const empty = full + kGemmStages;
-  uint64_t* const accum = empty + kGemmStages;
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  uint64_t* const acc_full = empty + kGemmStages;  // [2]: MMA -> epilogue
+  uint64_t* const acc_empty = acc_full + 2;        // [2]: epilogue (4 warps) -> MMA
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   uint32_t* const failed = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = (n + kGemmBN - 1) / kGemmBN;
-  const int tm = blockIdx.x / tiles_n, tn = blockIdx.x % tiles_n;
+  const int tiles_m = (m + kGemmBM - 1) / kGemmBM, tiles_n = (n + kGemmBN - 1) / kGemmBN;
+  const int tiles = tiles_m * tiles_n;
   const int kblocks = (k + kGemmBK - 1) / kGemmBK;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&map_a);
     prefetch_tmap(&map_b);
     for (int s = 0; s < kGemmStages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], 1);
-    mbar_init(accum, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&acc_full[i], 1), mbar_init(&acc_empty[i], 4);
     *failed = 0;
     fence_mbar_init();
   }
@@ -106,76 +127,101 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   if (warp == 0) {
     if (lane == 0) {  // ---- loader
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % kGemmStages;
-        const uint32_t ph = (uint32_t)(kb / kGemmStages) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u)) {
-          atomicExch(failed, 1u);
-          break;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        gemm_tile_coords(t, tiles_m, tiles_n, tm, tn);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u)) {
+            atomicExch(failed, 1u);
+            ok = false;
+            break;
+          }
+          uint8_t* stage = base + s * kGemmStageBytes;
+          mbar_expect_tx(&full[s], kGemmStageBytes);
+          tma_load_2d(stage, &map_a, kb * kGemmBK, tm * kGemmBM, &full[s]);
+          tma_load_2d(stage + kGemmATile, &map_b, kb * kGemmBK, tn * kGemmBN, &full[s]);
         }
-        uint8_t* stage = base + s * kGemmStageBytes;
-        mbar_expect_tx(&full[s], kGemmStageBytes);
-        tma_load_2d(stage, &map_a, kb * kGemmBK, tm * kGemmBM, &full[s]);
-        tma_load_2d(stage + kGemmATile, &map_b, kb * kGemmBK, tn * kGemmBN, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer
       const uint32_t idesc = gemm_instr_desc(fmt);
+      uint32_t it = 0;
       bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
-        const int s = kb % kGemmStages;
-        const uint32_t ph = (uint32_t)(kb / kGemmStages) & 1u;
-        if (!mbar_wait(&full[s], ph)) {
+      int i = 0;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
+        const uint32_t buf = (uint32_t)i & 1u, aph = ((uint32_t)i >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], aph ^ 1u)) {  // the epilogue has drained this accumulator
           atomicExch(failed, 1u);
-          ok = false;
           break;
         }
         tcgen05_fence_after();
-        const uint32_t sa = smem_u32(base + s * kGemmStageBytes);
-        const uint64_t da = gemm_smem_desc(sa), db = gemm_smem_desc(sa + kGemmATile);
+        const uint32_t acc = tmem + buf * (uint32_t)kGemmBN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
+          if (!mbar_wait(&full[s], ph)) {
+            atomicExch(failed, 1u);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(base + s * kGemmStageBytes);
+          const uint64_t da = gemm_smem_desc(sa), db = gemm_smem_desc(sa + kGemmATile);
 #pragma unroll
-        for (int j = 0; j < kGemmBK / 32; ++j)  // 32 bytes of K per instruction: the descriptor start moves by 32 >> 4
-          umma_f8(tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb > 0 || j > 0) ? 1u : 0u);
-        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+          for (int j = 0; j < kGemmBK / 32; ++j)  // 32 bytes of K per instruction: the descriptor start moves by 32 >> 4
+            umma_f8(acc, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);  // complete once every MMA issued so far has finished
       }
-      if (ok) umma_commit(accum);  // the accumulator is complete once every MMA issued so far has finished
     }
   } else {  // ---- epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
-    const int row = tm * kGemmBM + quarter * 32 + lane;
-    bool ok = mbar_wait(accum, 0);
-    if (!ok) atomicExch(failed, 1u);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    const float sb0 = rowwise ? 0.0f : b_scale[0];
+    int i = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
+      int tm, tn;
+      gemm_tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const uint32_t buf = (uint32_t)i & 1u, aph = ((uint32_t)i >> 1) & 1u;
+      bool ok = mbar_wait(&acc_full[buf], aph);
+      if (!ok) atomicExch(failed, 1u);
+      if (!__all_sync(0xffffffffu, ok)) break;
       tcgen05_fence_after();
+      const int row = tm * kGemmBM + quarter * 32 + lane;
       const float sa = rowwise ? (row < m ? a_scale[row] : 0.0f) : a_scale[0];
-      const float sb0 = rowwise ? 0.0f : b_scale[0];
 #pragma unroll 1
       for (int c0 = 0; c0 < kGemmBN; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)kGemmBN + (uint32_t)c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col0 = tn * kGemmBN + c0;
         if (row < m && col0 < n) {
           uint32_t o[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int c = col0 + 2 * i;
+          for (int j = 0; j < 16; ++j) {
+            const int c = col0 + 2 * j;
             const float s0 = rowwise ? __fmul_rn(sa, c < n ? b_scale[c] : 0.0f) : __fmul_rn(sa, sb0);
             const float s1 = rowwise ? __fmul_rn(sa, c + 1 < n ? b_scale[c + 1] : 0.0f) : s0;
-            const float v0 = __fmul_rn(__uint_as_float(r[2 * i]), s0), v1 = __fmul_rn(__uint_as_float(r[2 * i + 1]), s1);
-            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[i]) : "f"(v1), "f"(v0));
+            const float v0 = __fmul_rn(__uint_as_float(r[2 * j]), s0), v1 = __fmul_rn(__uint_as_float(r[2 * j + 1]), s1);
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(v1), "f"(v0));
           }
           uint16_t* dst = out + (int64_t)row * n + col0;
           if (col0 + 32 <= n && (n % 8) == 0) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) stg128(dst + 8 * i, make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
+            for (int j = 0; j < 4; ++j) stg128(dst + 8 * j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
           } else {
-            for (int i = 0; i < 32 && col0 + i < n; ++i) dst[i] = (uint16_t)(o[i >> 1] >> (16 * (i & 1)));
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < n) dst[j] = (uint16_t)(o[j >> 1] >> (16 * (j & 1)));
           }
         }
       }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);  // this warp's quarter of the accumulator has been read
     }
   }
   tcgen05_fence_before();
@@ -245,7 +291,9 @@ extern "C" int tnq_fp8_gemm(const void* a, const void* b, const float* a_scale, 
       return cuda_fail(cudaGetLastError());
     configured[dev] = 1;
   }
-  k_fp8_gemm<<<(unsigned)tiles, kGemmThreads, kGemmSmemBytes, stream>>>(
+  const int64_t sms = sm_count();
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  k_fp8_gemm<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
       map_a, map_b, a_scale, b_scale, rowwise ? 1 : 0, fp8_dtype == TNQ_FP8_E4M3 ? 0 : 1, (int)m, (int)n, (int)k,
       static_cast<uint16_t*>(out_bf16), status);
   return check_launch();
