@@ -74,7 +74,10 @@ __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.f
 // Tile t of the (tiles_m x tiles_n) grid in a grouped order: kGemmGroupM consecutive row-tiles are
 // swept across all column-tiles before the next group starts, so the tiles in flight at one
 // time share a small set of A and B panels in L2.
-constexpr int kGemmGroupM = 8;
+#ifndef TNQ_GEMM_GROUP_M
+#define TNQ_GEMM_GROUP_M 8
+#endif
+constexpr int kGemmGroupM = TNQ_GEMM_GROUP_M;
 __device__ __forceinline__ void gemm_tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_group = kGemmGroupM * tiles_n;
   const int group = t / per_group, in_group = t % per_group;
