@@ -611,7 +611,7 @@ def _bench_fp8_gemm(dev, res, timed, stream):
 
     from transformer_nuggets_b200 import _lib
 
-    m = n = k = 8192
+    m = n = k = int(os.environ.get("TNQ_BENCH_GEMM_SIZE", "8192"))  # a smaller cube for profiler captures
     g = torch.Generator(device=dev).manual_seed(4001)
     a = torch.randn(m, k, device=dev, generator=g).to(torch.float8_e4m3fn)
     b_nk = torch.randn(n, k, device=dev, generator=g).to(torch.float8_e4m3fn)

@@ -75,7 +75,7 @@ __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.f
 // swept across all column-tiles before the next group starts, so the tiles in flight at one
 // time share a small set of A and B panels in L2.
 #ifndef TNQ_GEMM_GROUP_M
-#define TNQ_GEMM_GROUP_M 8
+#define TNQ_GEMM_GROUP_M 16
 #endif
 constexpr int kGemmGroupM = TNQ_GEMM_GROUP_M;
 __device__ __forceinline__ void gemm_tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
