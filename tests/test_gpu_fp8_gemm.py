@@ -63,3 +63,56 @@ def test_argument_checks():
         matmul_persistent(a, torch.ones(16, 1, device=DEV), b.t(), torch.ones(1, 5, device=DEV))
     with pytest.raises(TypeError):
         matmul_persistent(a, one, b.t(), one, torch.float16)
+
+
+@pytest.mark.parametrize("row_wise", [False, True])
+def test_casts_feed_the_gemm_end_to_end(row_wise):
+    """bf16 activation and weight -> this library's casts -> this library's GEMM with the
+    reciprocal scales: close to the bf16 matmul within fp8 quantisation error."""
+    import transformer_nuggets_b200 as tn
+
+    g = torch.Generator(device=DEV).manual_seed(17)
+    x = torch.randn(512, 1024, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(768, 1024, device=DEV, generator=g) * 0.05).to(torch.bfloat16)  # stored [N, K]
+    if row_wise:
+        qx, sx = tn.rowwise_scaled_quant(x, torch.float8_e4m3fn)
+        qw, sw = tn.rowwise_scaled_quant(w, torch.float8_e4m3fn)
+        a_scale, b_scale = 1.0 / sx, (1.0 / sw).t().contiguous()
+    else:
+        qx, sx = tn.dynamic_scaled_quant_with_scale(x)
+        qw, sw = tn.dynamic_scaled_quant_with_scale(w)
+        a_scale, b_scale = 1.0 / sx, 1.0 / sw
+    got = matmul_persistent(qx, a_scale, qw.t(), b_scale, torch.bfloat16).float()
+    ref = x.float() @ w.float().t()
+    err = (got - ref).abs().max().item() / ref.abs().max().item()
+    assert err < 0.06, err
+
+
+def test_graph_capture_and_replay():
+    m, n, k = 256, 512, 512
+    a, b_nk = _operands(m, n, k, torch.float8_e4m3fn, 23)
+    a, b_nk = a.to(DEV), b_nk.to(DEV)
+    sa, sb = torch.tensor([1.0], device=DEV), torch.tensor([0.5], device=DEV)
+    c = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    side = torch.cuda.Stream()
+
+    def launch():
+        _lib.call("tnq_fp8_gemm", a.data_ptr(), b_nk.data_ptr(), sa.data_ptr(), sb.data_ptr(), 0, _lib.FP8_E4M3, m, n, k,
+                  c.data_ptr(), status.data_ptr(), side.cuda_stream)
+
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launch()
+    torch.cuda.synchronize()
+    first = c.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        launch()
+    c.zero_()
+    a.copy_((a.float() * 0.5).to(torch.float8_e4m3fn))  # new operand values, same buffers
+    graph.replay()
+    torch.cuda.synchronize()
+    want = oracle.fp8_matmul(a.cpu(), sa.cpu(), b_nk.cpu().t(), sb.cpu())
+    torch.testing.assert_close(c.cpu().float(), want.float(), rtol=2 ** -7, atol=0.5)
+    assert status.item() == 0 and not torch.equal(first, c)
