@@ -162,6 +162,16 @@ int tnq_fp8_gemm(const void* a, const void* b, const float* a_scale, const float
                  int fp8_dtype, int64_t m, int64_t n, int64_t k, void* out_bf16, uint32_t* status,
                  tnq_stream_t stream);
 
+/* MXFP8 GEMM on the block-scaled tensor-core path (tcgen05.mma kind::mxf8f6f4.block_scale):
+ *   out[m, n] = bf16( sum over 32-element blocks b of 2^(sa[m,b]-127) * 2^(sb[n,b]-127) * dot(a[m, b], b[n, b]) )
+ * a [M, K], b [N, K] e4m3 with K contiguous; sf_a, sf_b the E8M0 scales of [M, K/32] and
+ * [N, K/32] in the swizzled 128x4 layout (flat, padded to whole atoms), i.e. exactly what
+ * tnq_mxfp8_quantize / tnq_to_blocked write.  K % 128 == 0; all five buffers 16-byte aligned.
+ * The reference has no kernel for this shape class: its tests hand the same operands to
+ * `F.scaled_mm` with BlockWise1x32 + SWIZZLE_32_4_4 (test/test_mxfp8_tma.py:174-203). */
+int tnq_mxfp8_gemm(const void* a, const void* b, const void* sf_a, const void* sf_b, int64_t m, int64_t n,
+                   int64_t k, void* out_bf16, uint32_t* status, tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent
