@@ -494,6 +494,8 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_rmsnorm(dev, res, timed, peak, stream)
     if only == "fp8_gemm":  # tensor-core row; not part of the default run (a seconds-long dense GEMM loop)
         _bench_fp8_gemm(dev, res, timed, stream)
+    if only == "mxfp8_gemm":
+        _bench_mxfp8_gemm(dev, res, timed, stream)
     if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
         _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
     st = int(ws[_lib.WS_STATUS_WORD].item())
@@ -644,6 +646,45 @@ def _bench_fp8_gemm(dev, res, timed, stream):
         "note": f"e4m3 {m}x{n}x{k}, per-tensor scales, bf16 out; measured dense bf16 peak {bf16_peak} TF/s "
                 "(fp8 nominal is twice the bf16 figure)",
     }
+
+
+def _bench_mxfp8_gemm(dev, res, timed, stream):
+    """MXFP8 block-scaled GEMM, M = N = K = 8192, operands and swizzled scales from this library's
+    quantizer, with the library's block-scaled GEMM (F.scaled_mm, cuBLASLt) beside it."""
+    import torch
+
+    import transformer_nuggets_b200 as tn
+    from transformer_nuggets_b200 import _lib
+
+    m = n = k = int(os.environ.get("TNQ_BENCH_GEMM_SIZE", "8192"))
+    g = torch.Generator(device=dev).manual_seed(4002)
+    rx = tn.quantize_mxfp8(torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16), swizzle=True)
+    rw = tn.quantize_mxfp8(torch.randn(n, k, device=dev, generator=g).to(torch.bfloat16), swizzle=True)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    status = _lib.workspace(dev).data_ptr() + 4 * _lib.WS_STATUS_WORD
+
+    def ours(_):
+        _lib.call("tnq_mxfp8_gemm", rx.q_row.data_ptr(), rw.q_row.data_ptr(), rx.scale_row.data_ptr(),
+                  rw.scale_row.data_ptr(), m, n, k, c.data_ptr(), status, stream)
+
+    flops = 2.0 * m * n * k
+    ms = timed(ours, [None])
+    r = {"us": ms * 1e3, "TFLOPs": flops / (ms * 1e-3) / 1e12,
+         "note": f"e4m3 + E8M0 1x32 blocks, {m}x{n}x{k}, swizzled scales straight from the quantizer, bf16 out"}
+    try:
+        from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+
+        def library(_):
+            scaled_mm(rx.q_row, rw.q_row.t(), scale_a=[rx.scale_row.view(torch.float8_e8m0fnu)],
+                      scale_recipe_a=[ScalingType.BlockWise1x32], swizzle_a=[SwizzleType.SWIZZLE_32_4_4],
+                      scale_b=[rw.scale_row.view(torch.float8_e8m0fnu)], scale_recipe_b=[ScalingType.BlockWise1x32],
+                      swizzle_b=[SwizzleType.SWIZZLE_32_4_4], output_dtype=torch.bfloat16)
+
+        ms_lib = timed(library, [None])
+        r.update({"library_us": ms_lib * 1e3, "library_TFLOPs": flops / (ms_lib * 1e-3) / 1e12, "frac_of_library": ms_lib / ms})
+    except ImportError:
+        r["library_us"] = None
+    res["mxfp8_gemm"] = r
 
 
 def _bench_gemv(dev, res, timed, peak, stream, which=None):

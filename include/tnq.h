@@ -172,6 +172,18 @@ int tnq_fp8_gemm(const void* a, const void* b, const float* a_scale, const float
 int tnq_mxfp8_gemm(const void* a, const void* b, const void* sf_a, const void* sf_b, int64_t m, int64_t n,
                    int64_t k, void* out_bf16, uint32_t* status, tnq_stream_t stream);
 
+/* NVFP4 GEMM on the block-scaled tensor-core path (tcgen05.mma kind::mxf4nvf4.block_scale.block16):
+ *   out[m, n] = bf16( ga * gb * sum over 16-element blocks b of sa[m,b] * sb[n,b] * dot(a[m, b], b[n, b]) )
+ * a_packed [M, K/2], b_packed [N, K/2]: two e2m1 codes per byte, low nibble first, K contiguous;
+ * sf_a, sf_b: E4M3 block scales of [M, K/16] and [N, K/16] in the swizzled 128x4 layout; a_global,
+ * b_global: fp32 tensor-wide scales in the decode direction (nullable = 1), i.e. exactly what
+ * tnq_nvfp4_quantize writes.  K % 256 == 0; buffers 16-byte aligned.
+ * The reference has no kernel for this shape class: its tests hand the same operands to
+ * `F.scaled_mm` with BlockWise1x16 + TensorWise scaling (test/test_nvfp4_tma.py:511-548). */
+int tnq_nvfp4_gemm(const void* a_packed, const void* b_packed, const void* sf_a, const void* sf_b,
+                   const float* a_global, const float* b_global, int64_t m, int64_t n, int64_t k, void* out_bf16,
+                   uint32_t* status, tnq_stream_t stream);
+
 /* amax -> scale = fp8_max / max(amax, 1e-12) -> saturated cast.  A tensor that fits in
  * the shared memory of all SMs together (and is a multiple of 16 bytes) takes one
  * cooperative launch that reads x from HBM once; larger tensors take two dependent

@@ -59,6 +59,7 @@ SIGNATURES = {
     "tnq_swiglu_mxfp8": [_p, _p, _i64, _i64, _p, _p, _i, _i, _p, _p],
     "tnq_fp8_gemm": [_p, _p, _p, _p, _i, _i, _i64, _i64, _i64, _p, _p, _p],
     "tnq_mxfp8_gemm": [_p, _p, _p, _p, _i64, _i64, _i64, _p, _p, _p],
+    "tnq_nvfp4_gemm": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p, _p],
     "tnq_delayed_scale_update": [_p, _p, _p, _i64, _i, _i, _p],
     "tnq_mxfp8_gemv": [_p, _p, _p, _p, _i64, _i64, _i, _p, _p],
     "tnq_nvfp4_gemv": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p, _p],
