@@ -496,6 +496,8 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_fp8_gemm(dev, res, timed, stream)
     if only == "mxfp8_gemm":
         _bench_mxfp8_gemm(dev, res, timed, stream)
+    if only == "nvfp4_gemm":
+        _bench_nvfp4_gemm(dev, res, timed, stream)
     if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
         _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
     st = int(ws[_lib.WS_STATUS_WORD].item())
@@ -685,6 +687,48 @@ def _bench_mxfp8_gemm(dev, res, timed, stream):
     except ImportError:
         r["library_us"] = None
     res["mxfp8_gemm"] = r
+
+
+def _bench_nvfp4_gemm(dev, res, timed, stream):
+    """NVFP4 block-scaled GEMM, M = N = K = 8192, operands, swizzled E4M3 scales and global scales from
+    this library's quantizer, with the library's block-scaled GEMM (F.scaled_mm) beside it."""
+    import torch
+
+    import transformer_nuggets_b200 as tn
+    from transformer_nuggets_b200 import _lib
+
+    m = n = k = int(os.environ.get("TNQ_BENCH_GEMM_SIZE", "8192"))
+    g = torch.Generator(device=dev).manual_seed(4003)
+    a = tn.quantize_nvfp4(torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16), swizzle=True)
+    b = tn.quantize_nvfp4(torch.randn(n, k, device=dev, generator=g).to(torch.bfloat16), swizzle=True)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    status = _lib.workspace(dev).data_ptr() + 4 * _lib.WS_STATUS_WORD
+
+    def ours(_):
+        _lib.call("tnq_nvfp4_gemm", a.packed.data_ptr(), b.packed.data_ptr(), a.block_scales.data_ptr(),
+                  b.block_scales.data_ptr(), a.global_scale.data_ptr(), b.global_scale.data_ptr(), m, n, k, c.data_ptr(),
+                  status, stream)
+
+    flops = 2.0 * m * n * k
+    ms = timed(ours, [None])
+    r = {"us": ms * 1e3, "TFLOPs": flops / (ms * 1e-3) / 1e12,
+         "note": f"packed e2m1 + E4M3 1x16 blocks + global scales, {m}x{n}x{k}, operands straight from the quantizer, bf16 out"}
+    try:
+        from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+
+        def library(_):
+            scaled_mm(a.packed, b.packed.t(), scale_a=[a.block_scales, a.global_scale],
+                      scale_recipe_a=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
+                      swizzle_a=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
+                      scale_b=[b.block_scales, b.global_scale],
+                      scale_recipe_b=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
+                      swizzle_b=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE], output_dtype=torch.bfloat16)
+
+        ms_lib = timed(library, [None])
+        r.update({"library_us": ms_lib * 1e3, "library_TFLOPs": flops / (ms_lib * 1e-3) / 1e12, "frac_of_library": ms_lib / ms})
+    except ImportError:
+        r["library_us"] = None
+    res["nvfp4_gemm"] = r
 
 
 def _bench_gemv(dev, res, timed, peak, stream, which=None):
