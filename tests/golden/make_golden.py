@@ -173,4 +173,8 @@ def main(ref_root, only=None):
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     only = "rmsnorm" if "--only" in sys.argv and "rmsnorm" in sys.argv else None
-    main(args[0] if args and args[0] != "rmsnorm" else "/root/reference", only)
+    roots = [a for a in args if a != "rmsnorm"]
+    root = roots[0] if roots else os.environ.get("TNQ_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: make_golden.py /path/to/transformer_nuggets [--only rmsnorm]  (or set TNQ_REFERENCE_ROOT)")
+    main(root, only)
