@@ -116,3 +116,24 @@ def test_graph_capture_and_replay():
     want = oracle.fp8_matmul(a.cpu(), sa.cpu(), b_nk.cpu().t(), sb.cpu())
     torch.testing.assert_close(c.cpu().float(), want.float(), rtol=2 ** -7, atol=0.5)
     assert status.item() == 0 and not torch.equal(first, c)
+
+
+def test_output_on_a_16_byte_boundary_only():
+    """The epilogue writes 256 bits per lane when every output row starts on a 32-byte boundary
+    and 128 bits otherwise; both paths give the same bits."""
+    m, n, k = 256, 512, 256
+    a, b_nk = _operands(m, n, k, torch.float8_e4m3fn, 11)
+    a, b_nk = a.to(DEV), b_nk.to(DEV)
+    one = torch.ones(1, device=DEV)
+    want = matmul_persistent(a, one, b_nk.t(), one)
+    dev = torch.device(DEV, 0)
+    buf = torch.zeros(m * n + 16, dtype=torch.bfloat16, device=DEV)
+    assert buf.data_ptr() % 32 == 0
+    shifted = buf[8:8 + m * n]  # 16 bytes past a 32-byte boundary
+    with torch.cuda.device(dev):
+        _lib.call("tnq_fp8_gemm", a.data_ptr(), b_nk.data_ptr(), one.data_ptr(), one.data_ptr(), 0,
+                  _lib.FP8_DTYPES[a.dtype], m, n, k, shifted.data_ptr(),
+                  _lib.workspace(dev).data_ptr() + 4 * _lib.WS_STATUS_WORD, _lib.stream_ptr(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(shifted.view(m, n).view(torch.int16), want.view(torch.int16))
+    assert int(buf[:8].view(torch.int16).abs().sum()) == 0 and int(buf[8 + m * n:].view(torch.int16).abs().sum()) == 0

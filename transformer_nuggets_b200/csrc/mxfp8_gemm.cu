@@ -210,6 +210,8 @@ __global__ void __launch_bounds__(kMxgThreads, 1)
       }
     }
   } else {  // ---- epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
+    // every output row starts on a 32-byte boundary: 256-bit stores are legal
+    const bool wide_rows = (n % 16) == 0 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
     const int quarter = warp & 3;
     int i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
@@ -234,7 +236,10 @@ __global__ void __launch_bounds__(kMxgThreads, 1)
             asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
           }
           uint16_t* dst = out + (int64_t)row * n + col0;
-          if (col0 + 32 <= n && (n % 8) == 0) {
+          if (col0 + 32 <= n && wide_rows) {  // two whole 32-byte sectors per lane and instruction
+            stg256(dst, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
+            stg256(dst + 16, o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]);
+          } else if (col0 + 32 <= n && (n % 8) == 0) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) stg128(dst + 8 * j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
           } else {
