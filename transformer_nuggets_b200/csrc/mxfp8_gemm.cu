@@ -27,7 +27,8 @@ constexpr int kMxgATile = kMxgBM * kMxgBK, kMxgBTile = kMxgBN * kMxgBK;
 constexpr int kMxgSfA = 512, kMxgSfB = 1024;  // one scale atom for the 128 rows of A, two for the 256 rows of B
 constexpr int kMxgStageData = kMxgATile + kMxgBTile + kMxgSfA + kMxgSfB;
 constexpr int kMxgStageBytes = 51200;  // kMxgStageData rounded up to a multiple of 1024 (tile alignment)
-constexpr int kMxgThreads = 192;
+constexpr int kMxgEpilogueWarps = 8;  // two per tensor-memory lane quarter: columns 0..127 and 128..255 of the tile
+constexpr int kMxgThreads = 64 + 32 * kMxgEpilogueWarps;  // + the loader warp and the MMA warp
 constexpr int kMxgTmemCols = 512;  // one 128 x 256 fp32 accumulator + 12 columns of scale bytes (power of two)
 constexpr int kMxgSfCol = 256;     // scale columns: A at +0 .. +3, B at +4 .. +11
 constexpr int kMxgSmemBytes = kMxgStages * kMxgStageBytes + 1024 /* alignment */ + 128 /* barriers */;
@@ -103,8 +104,9 @@ __device__ __forceinline__ void mxg_mbar_arrive(uint64_t* bar) {
 }
 
 // Persistent: CTA c computes tiles c, c + gridDim.x, ...  One accumulator (256 columns) plus the
-// scale columns fill the tensor-memory allocation, so the epilogue of a tile is not overlapped
-// with the next tile's MMAs here.  Measured alternatives: 128 x 192 tiles with two accumulators
+// scale columns fill the tensor-memory allocation, so only the stores of a tile's epilogue are
+// overlapped with the next tile's MMAs: eight warps first drain the accumulator into registers
+// and release it.  Measured alternatives: 128 x 192 tiles with two accumulators
 // (the scale columns of a tile then start 0 or 2 columns into an atom) overlap the epilogue but
 // re-read more of A per output and were 13-16 % slower; 128 x 224 tiles would need scale columns
 // starting on an odd column, which the MMA does not accept.
@@ -117,7 +119,7 @@ __global__ void __launch_bounds__(kMxgThreads, 1)
   uint64_t* const full = reinterpret_cast<uint64_t*>(base + kMxgStages * kMxgStageBytes);
   uint64_t* const empty = full + kMxgStages;
   uint64_t* const acc_full = empty + kMxgStages;  // [2]: MMA -> epilogue
-  uint64_t* const acc_empty = acc_full + 2;        // [2]: epilogue (4 warps) -> MMA
+  uint64_t* const acc_empty = acc_full + 2;        // [2]: epilogue (8 warps) -> MMA
   uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   uint32_t* const failed = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -129,7 +131,7 @@ __global__ void __launch_bounds__(kMxgThreads, 1)
     prefetch_tmap(&map_a);
     prefetch_tmap(&map_b);
     for (int s = 0; s < kMxgStages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], 1);
-    for (int i = 0; i < 2; ++i) mbar_init(&acc_full[i], 1), mbar_init(&acc_empty[i], 4);
+    for (int i = 0; i < 2; ++i) mbar_init(&acc_full[i], 1), mbar_init(&acc_empty[i], kMxgEpilogueWarps);
     *failed = 0;
     fence_mbar_init();
   }
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(kMxgThreads, 1)
   } else {  // ---- epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
     // every output row starts on a 32-byte boundary: 256-bit stores are legal
     const bool wide_rows = (n % 16) == 0 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     int i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
       int tm, tn;
@@ -223,35 +225,43 @@ __global__ void __launch_bounds__(kMxgThreads, 1)
       if (!__all_sync(0xffffffffu, ok)) break;
       mxg_fence_after();
       const int row = tm * kMxgBM + quarter * 32 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kMxgBN; c0 += 32) {
+      // Drain this warp's 32 rows x 128 columns into registers as packed bf16, hand the accumulator
+      // back to the MMA issuer, then store: the stores overlap the next tile's MMAs.
+      uint32_t o[kMxgBN / 4];
+#pragma unroll
+      for (int c = 0; c < kMxgBN / 64; ++c) {
         uint32_t r[32];
-        mxg_tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)kMxgBN + (uint32_t)c0, r);
+        mxg_tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)kMxgBN + (uint32_t)(128 * half + 32 * c), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col0 = tn * kMxgBN + c0;
-        if (row < m && col0 < n) {
-          uint32_t o[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
-          }
-          uint16_t* dst = out + (int64_t)row * n + col0;
-          if (col0 + 32 <= n && wide_rows) {  // two whole 32-byte sectors per lane and instruction
-            stg256(dst, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
-            stg256(dst + 16, o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]);
-          } else if (col0 + 32 <= n && (n % 8) == 0) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) stg128(dst + 8 * j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < n) dst[j] = (uint16_t)(o[j >> 1] >> (16 * (j & 1)));
-          }
+        for (int j = 0; j < 16; ++j) {
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[16 * c + j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
         }
       }
       mxg_fence_before();
       __syncwarp();
-      if (lane == 0) mxg_mbar_arrive(&acc_empty[buf]);  // this warp's quarter of the accumulator has been read
+      if (lane == 0) mxg_mbar_arrive(&acc_empty[buf]);  // this warp's part of the accumulator has been read
+      if (row < m) {
+#pragma unroll
+        for (int c = 0; c < kMxgBN / 64; ++c) {
+          const int col0 = tn * kMxgBN + 128 * half + 32 * c;
+          if (col0 < n) {
+            uint16_t* dst = out + (int64_t)row * n + col0;
+            const uint32_t* oc = o + 16 * c;
+            if (col0 + 32 <= n && wide_rows) {  // two whole 32-byte sectors per lane and instruction
+              stg256(dst, oc[0], oc[1], oc[2], oc[3], oc[4], oc[5], oc[6], oc[7]);
+              stg256(dst + 16, oc[8], oc[9], oc[10], oc[11], oc[12], oc[13], oc[14], oc[15]);
+            } else if (col0 + 32 <= n && (n % 8) == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) stg128(dst + 8 * j, make_uint4(oc[4 * j], oc[4 * j + 1], oc[4 * j + 2], oc[4 * j + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < n) dst[j] = (uint16_t)(oc[j >> 1] >> (16 * (j & 1)));
+            }
+          }
+        }
+      }
     }
   }
   mxg_fence_before();
