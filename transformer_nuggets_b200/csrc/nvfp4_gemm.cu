@@ -9,6 +9,10 @@
 // buffer: one 2 KiB bulk copy for A and two for the 256 rows of B per stage.  Each of the four
 // MMAs of a stage (tcgen05.mma kind::mxf4nvf4.block_scale.block16, K = 64) consumes one whole
 // atom per 128 rows (four scale bytes per row), moved to tensor memory by tcgen05.cp.  The
+// twelve copies of a stage are issued by a lane of their own, one stage ahead of the MMAs and
+// into alternating sets of scale columns (its tcgen05.commit tells the MMA lane when a set is
+// filled; the MMAs' commit on the stage tells it when a set may be overwritten): with the copies
+// in front of the MMAs in one lane's instruction stream the kernel was 3-9 % slower.  The
 // global scales are applied to the fp32 accumulator in the epilogue.
 #include <cuda.h>
 
@@ -23,9 +27,9 @@ constexpr int kNvgSfA = 2048, kNvgSfB = 4096;  // four scale atoms (one per MMA)
 constexpr int kNvgStageData = kNvgATile + kNvgBTile + kNvgSfA + kNvgSfB;
 constexpr int kNvgStageBytes = 56320;  // kNvgStageData rounded up to a multiple of 1024 (tile alignment)
 constexpr int kNvgEpilogueWarps = 8;  // two per tensor-memory lane quarter: columns 0..127 and 128..255 of the tile
-constexpr int kNvgThreads = 64 + 32 * kNvgEpilogueWarps;  // + the loader warp and the MMA warp
-constexpr int kNvgTmemCols = 512;  // one 128 x 256 fp32 accumulator + 48 columns of scale bytes (power of two)
-constexpr int kNvgSfCol = 256;     // scale columns: A at +4j (MMA j of a stage), B at +16 + 8j (+4 for rows 128..255)
+constexpr int kNvgThreads = 96 + 32 * kNvgEpilogueWarps;  // + the loader warp, the MMA warp and the scale-copier warp
+constexpr int kNvgTmemCols = 512;  // one 128 x 256 fp32 accumulator + two sets of 48 scale columns (power of two)
+constexpr int kNvgSfCol = 256;     // scale set p at +64p: A at +4j (MMA j of a stage), B at +16 + 8j (+4 for rows 128..255)
 constexpr int kNvgSmemBytes = kNvgStages * kNvgStageBytes + 1024 /* alignment */ + 128 /* barriers */;
 
 // shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
@@ -115,7 +119,8 @@ __global__ void __launch_bounds__(kNvgThreads, 1)
   uint64_t* const empty = full + kNvgStages;
   uint64_t* const acc_full = empty + kNvgStages;  // [2]: MMA -> epilogue
   uint64_t* const acc_empty = acc_full + 2;        // [2]: epilogue (8 warps) -> MMA
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* const sfready = acc_empty + 2;         // [2]: scale copier -> MMA, one per set of scale columns
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(sfready + 2);
   uint32_t* const failed = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (m + kNvgBM - 1) / kNvgBM, tiles_n = (n + kNvgBN - 1) / kNvgBN;
@@ -127,6 +132,7 @@ __global__ void __launch_bounds__(kNvgThreads, 1)
     prefetch_tmap(&map_b);
     for (int s = 0; s < kNvgStages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], 1);
     for (int i = 0; i < 2; ++i) mbar_init(&acc_full[i], 1), mbar_init(&acc_empty[i], kNvgEpilogueWarps);
+    for (int i = 0; i < 2; ++i) mbar_init(&sfready[i], 1);
     *failed = 0;
     fence_mbar_init();
   }
@@ -171,44 +177,50 @@ __global__ void __launch_bounds__(kNvgThreads, 1)
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {  // ---- MMA issuer
-      uint32_t it = 0;
-      bool ok = true;
-      int i = 0;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
-        const uint32_t buf = 0u, aph = (uint32_t)i & 1u;  // one accumulator: tensor memory also holds the scales
-        if (!mbar_wait(&acc_empty[buf], aph ^ 1u)) {  // the epilogue has drained the accumulator
-          atomicExch(failed, 1u);
-          break;
+    if (lane == 0) {  // ---- MMA issuer; the scale columns are filled by the copier warp
+      const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+      const uint32_t total = (uint32_t)my_tiles * (uint32_t)kblocks;
+      const uint32_t idesc = nvg_instr_desc();
+      uint32_t tile_i = 0;
+      for (uint32_t it = 0; it < total; ++it) {
+        const uint32_t kb = it % (uint32_t)kblocks;
+        if (kb == 0) {
+          if (!mbar_wait(&acc_empty[0], (tile_i & 1u) ^ 1u)) { atomicExch(failed, 1u); break; }
         }
+        const uint32_t s = it % kNvgStages, ph = (it / kNvgStages) & 1u;
+        if (!mbar_wait(&full[s], ph) || !mbar_wait(&sfready[it & 1u], (it >> 1) & 1u)) { atomicExch(failed, 1u); break; }
         nvg_fence_after();
-        const uint32_t acc = tmem + buf * (uint32_t)kNvgBN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t s = it % kNvgStages, ph = (it / kNvgStages) & 1u;
-          if (!mbar_wait(&full[s], ph)) {
-            atomicExch(failed, 1u);
-            ok = false;
-            break;
-          }
-          nvg_fence_after();
-          const uint32_t sa = smem_u32(base + s * kNvgStageBytes);
-          const uint64_t da = nvg_smem_desc(sa), db = nvg_smem_desc(sa + kNvgATile);
-          // this stage's scale atoms -> tensor memory (executed in order with the MMAs that read them)
-          const uint32_t sfs = sa + kNvgATile + kNvgBTile;
+        const uint32_t sa = smem_u32(base + s * kNvgStageBytes);
+        const uint64_t da = nvg_smem_desc(sa), db = nvg_smem_desc(sa + kNvgATile);
+        const uint32_t set = tmem + kNvgSfCol + 64u * (it & 1u);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            nvg_sf_copy(tmem + kNvgSfCol + 4 * j, nvg_sf_desc(sfs + 512 * j));
-            nvg_sf_copy(tmem + kNvgSfCol + 16 + 8 * j, nvg_sf_desc(sfs + 2048 + 512 * j));
-            nvg_sf_copy(tmem + kNvgSfCol + 16 + 8 * j + 4, nvg_sf_desc(sfs + 4096 + 512 * j));
-          }
-          const uint32_t idesc = nvg_instr_desc();
+        for (int j = 0; j < kNvgBK / 32; ++j)
+          umma_nvf4(tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, set + 4 * j, set + 16 + 8 * j,
+                    (kb > 0 || j > 0) ? 1u : 0u);
+        nvg_commit(&empty[s]);
+        if (kb == (uint32_t)kblocks - 1) { nvg_commit(&acc_full[0]); ++tile_i; }
+      }
+    }
+  } else if (warp == 2 + kNvgEpilogueWarps) {
+    if (lane == 0) {  // ---- scale copier: shared memory -> the set of scale columns of iteration it
+      const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+      const uint32_t total = (uint32_t)my_tiles * (uint32_t)kblocks;
+      for (uint32_t it = 0; it < total; ++it) {
+        const uint32_t s = it % kNvgStages, ph = (it / kNvgStages) & 1u;
+        bool ok = mbar_wait(&full[s], ph);
+        // the MMAs of iteration it - 2 read this set of columns: their commit completes empty[(it - 2) % stages]
+        if (ok && it >= 2) ok = mbar_wait(&empty[(it - 2) % kNvgStages], ((it - 2) / kNvgStages) & 1u);
+        if (!ok) { atomicExch(failed, 1u); break; }
+        nvg_fence_after();
+        const uint32_t sfs = smem_u32(base + s * kNvgStageBytes) + kNvgATile + kNvgBTile;
+        const uint32_t set = tmem + kNvgSfCol + 64u * (it & 1u);
 #pragma unroll
-          for (int j = 0; j < kNvgBK / 32; ++j)  // 64 elements (32 bytes) and one scale atom per 128 rows per instruction
-            umma_nvf4(acc, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, tmem + kNvgSfCol + 4 * j,
-                      tmem + kNvgSfCol + 16 + 8 * j, (kb > 0 || j > 0) ? 1u : 0u);
-          nvg_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+        for (int j = 0; j < 4; ++j) {
+          nvg_sf_copy(set + 4 * j, nvg_sf_desc(sfs + 512 * j));
+          nvg_sf_copy(set + 16 + 8 * j, nvg_sf_desc(sfs + 2048 + 512 * j));
+          nvg_sf_copy(set + 16 + 8 * j + 4, nvg_sf_desc(sfs + 4096 + 512 * j));
         }
-        if (ok) nvg_commit(&acc_full[buf]);  // complete once every MMA issued so far has finished
+        nvg_commit(&sfready[it & 1u]);
       }
     }
   } else {  // ---- epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
