@@ -36,13 +36,16 @@ def test_matches_dequantised_matmul(m, n, k):
     torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2 ** -6, atol=2 ** -8 * scale)
 
 
-def test_against_library_block_scaled_mm():
+# (4096, 8192) gives 1024 tiles: every CTA of the persistent grid walks several tiles, so the stage
+# ring, the single accumulator's hand-over and the scale-column sets wrap across tile boundaries;
+# K = 640 / 768 makes the number of stages per tile odd or not a multiple of the ring depth
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 1024), (4096, 8192, 640), (2304, 4352, 1536)])
+def test_against_library_block_scaled_mm(m, n, k):
     try:
         from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
     except ImportError:
         pytest.skip("this torch has no block-scaled scaled_mm")
 
-    m, n, k = 512, 1024, 1024
     x, w = _case(m, n, k, 9)
     rx = tn.quantize_mxfp8(x.to(DEV), swizzle=True)
     rw = tn.quantize_mxfp8(w.to(DEV), swizzle=True)
@@ -74,12 +77,12 @@ def test_nvfp4_matches_dequantised_matmul(m, n, k):
     torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2 ** -6, atol=2 ** -8 * scale)
 
 
-def test_nvfp4_against_library_block_scaled_mm():
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 2048), (4096, 8192, 768), (2304, 4352, 1280)])
+def test_nvfp4_against_library_block_scaled_mm(m, n, k):
     try:
         from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
     except ImportError:
         pytest.skip("this torch has no block-scaled scaled_mm")
-    m, n, k = 512, 1024, 2048
     x, w = _case(m, n, k, 10)
     a, b = tn.quantize_nvfp4(x.to(DEV), swizzle=True), tn.quantize_nvfp4(w.to(DEV), swizzle=True)
     got = nvfp4_scaled_mm(a.packed, b.packed.t(), a.block_scales, b.block_scales, a.global_scale, b.global_scale)
