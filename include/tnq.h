@@ -42,7 +42,14 @@ typedef enum { TNQ_SCALE_IS_SCALE = 0, TNQ_SCALE_IS_AMAX = 1 } tnq_scale_source;
  * leave it ready for the next call.  Two calls that share a workspace must be
  * ordered (same stream); use one workspace per concurrent stream.
  * Layout (uint32 words): [0] ticket  [1] amax as fp32 bits  [2] scale (fp32)
- * [3] device status  [16..] per-CTA partial maxima. */
+ * [3] device status  [4..7] grid-barrier words of the single-launch cast
+ * [16..] per-CTA partial maxima.
+ * Device status: every wait inside a kernel is bounded (about one second); a wait
+ * that gives up stores TNQ_ETIMEOUT in word [3] (or in the `status` word an entry
+ * point takes) and the kernel returns with its outputs incomplete.  Nothing reads
+ * the word for the caller: read it after synchronising the stream.  A kernel that
+ * left early may not have rewound words [0] and [4..7], so after a TNQ_ETIMEOUT
+ * zero the first 64 bytes of the workspace before using it again. */
 #define TNQ_WORKSPACE_BYTES 16384
 #define TNQ_WS_AMAX_WORD 1
 #define TNQ_WS_SCALE_WORD 2

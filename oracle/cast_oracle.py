@@ -94,10 +94,13 @@ def fp8_dynamic_quant(a: torch.Tensor, fp8_dtype: torch.dtype):
 def fp8_rowwise_quant(a: torch.Tensor, fp8_dtype: torch.dtype):
     """Row-wise dynamic cast -> (fp8 [M, K], fp32 scale [M, 1]).
 
-    Parity: restatement.  The reference has no rowwise cast, only the consumer
-    contract - a per-row fp32 scale of shape [M, 1] (fp8/fp8_matmul.py:50-61).
-    The per-tensor formula of fp8/scaled_quant.py:95-102 / :132-135 is applied
-    to each row.  The returned scale is the quantisation-direction one
+    Parity: pinned through ``eager_scaled_quant`` (fp8/scaled_quant.py:78-102)
+    called once per row with that row's ``[1]``-shaped scale and
+    ``saturated=True`` (fixture ``tests/golden/fp8_rowwise.npz``).  The
+    reference has no rowwise cast of its own, only the consumer contract - a
+    per-row fp32 scale of shape [M, 1] (fp8/fp8_matmul.py:50-61); the scale
+    rule ``max / clamp(amax_r, 1e-12)`` is the per-tensor one of :132-135 at
+    row granularity.  The returned scale is the quantisation-direction one
     (``max/amax_r``), like the per-tensor scale.
     """
     assert a.dim() == 2

@@ -15,6 +15,8 @@ fp8 as uint8).  Functions called, by reference path:
 * cute/nvfp4_tma.py:941    pack_nvfp4_codes
 * cute/nvfp4_tma.py:946    swizzle_nvfp4_scales
 * examples/rms_norm_fusion_profile.py:26  handwritten_rms_norm  (``--only rmsnorm`` writes just this one)
+* fp8/scaled_quant.py:78   eager_scaled_quant once per ROW with that row's scale as a ``[1]`` tensor: the
+                           row-wise cast is the per-tensor cast at row granularity (``--only rowwise``)
 """
 
 import os
@@ -58,11 +60,49 @@ def rms_norm_fixture(ref_root):
     np.savez_compressed(os.path.join(HERE, "rms_norm.npz"), **out)
 
 
+def rowwise_fixture():
+    """Row-wise cast through the reference's ``eager_scaled_quant`` (fp8/scaled_quant.py:78-102), one call
+    per row: ``scale_r = finfo.max / max(amax_r, 1e-12)`` as one fp32 division, handed over with shape
+    ``[1]`` (a 0-dim scale would make the product bf16), ``saturated=True``.  Rows: seeded normal data
+    with per-row sigma, an all-zero row, a row with one outlier, a row holding a NaN, a row holding an
+    infinity, a row of bf16 subnormals."""
+    from transformer_nuggets.fp8.scaled_quant import eager_scaled_quant
+
+    g = torch.Generator().manual_seed(20245)
+    rows, cols = 40, 384
+    x = torch.randn(rows, cols, generator=g) * torch.exp2(torch.rand(rows, 1, generator=g) * 12 - 6)
+    x[3] = 0.0
+    x[5, 17] = 3.0e4
+    x[7, 100] = float("nan")
+    x[9, 0] = float("-inf")
+    x[11] = x[11] * 1e-39
+    xb = x.to(torch.bfloat16)
+    out = {"x_bits": bf16_bits(xb)}
+    for dname, dt in (("e4m3", torch.float8_e4m3fn), ("e5m2", torch.float8_e5m2)):
+        fmax = torch.tensor(torch.finfo(dt).max, dtype=torch.float32)
+        q = torch.empty(rows, cols, dtype=torch.uint8)
+        scales = torch.empty(rows, 1, dtype=torch.float32)
+        for r in range(rows):
+            row = xb[r : r + 1]
+            amax = row.abs().max().float()
+            scale = (fmax / torch.clamp(amax, min=1e-12)).reshape(1)
+            am = torch.tensor([-1.0])
+            q[r] = eager_scaled_quant(row, scale, am, dt, True).view(torch.uint8)[0]
+            scales[r, 0] = scale[0]
+        out[f"q_{dname}"] = q.numpy()
+        out[f"scale_{dname}"] = scales.numpy()
+    np.savez_compressed(os.path.join(HERE, "fp8_rowwise.npz"), **out)
+
+
 def main(ref_root, only=None):
     sys.path.insert(0, ref_root)
     if only == "rmsnorm":
         rms_norm_fixture(ref_root)
         print("rms_norm.npz written to", HERE)
+        return
+    if only == "rowwise":
+        rowwise_fixture()
+        print("fp8_rowwise.npz written to", HERE)
         return
     from transformer_nuggets.cute.mxfp8_tma import quantize_mxfp8_tensor
     from transformer_nuggets.cute.nvfp4_tma import pack_nvfp4_codes, swizzle_nvfp4_scales
@@ -167,14 +207,15 @@ def main(ref_root, only=None):
         codes=codes.numpy(), packed=packed.numpy(), scales=scales.numpy(), swizzled=sw.numpy(),
     )
     rms_norm_fixture(ref_root)
+    rowwise_fixture()
     print("golden fixtures written to", HERE)
 
 
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    only = "rmsnorm" if "--only" in sys.argv and "rmsnorm" in sys.argv else None
-    roots = [a for a in args if a != "rmsnorm"]
+    only = next((a for a in ("rmsnorm", "rowwise") if "--only" in sys.argv and a in sys.argv), None)
+    roots = [a for a in args if a not in ("rmsnorm", "rowwise")]
     root = roots[0] if roots else os.environ.get("TNQ_REFERENCE_ROOT")
     if not root:
-        sys.exit("usage: make_golden.py /path/to/transformer_nuggets [--only rmsnorm]  (or set TNQ_REFERENCE_ROOT)")
+        sys.exit("usage: make_golden.py /path/to/transformer_nuggets [--only rmsnorm|rowwise]  (or set TNQ_REFERENCE_ROOT)")
     main(root, only)

@@ -82,3 +82,26 @@ def test_argument_checks():
         scaled_quant_transpose(torch.zeros(2, 4, 8, dtype=torch.bfloat16, device=DEV), s)
     q, q_t = scaled_quant_transpose(torch.zeros(0, 8, dtype=torch.bfloat16, device=DEV), s)
     assert q.shape == (0, 8) and q_t.shape == (8, 0)
+
+
+@pytest.mark.parametrize("start", [float("nan"), -1.0, 0.0, 1.0e9])
+def test_abs_max_history_word_same_rule_in_both_casts(start):
+    """abs_max becomes max(abs_max, max|x|) on the bit patterns in the plain and in the transposing
+    cast alike: a NaN already stored stays, a negative starting value (-1.0, as the reference's
+    tests use) loses, a larger previous value is kept."""
+    x = _data(256, 384, 11, special=False).to(DEV)
+    scale = torch.tensor([0.5], device=DEV)
+    am1 = torch.tensor([start], device=DEV)
+    am2 = torch.tensor([start], device=DEV)
+    scaled_quant(x, scale, am1, torch.float8_e4m3fn, True)
+    scaled_quant_transpose(x, scale, am2, torch.float8_e4m3fn, True)
+    true_amax = x.abs().max().float().item()
+    if start != start:
+        assert torch.isnan(am1).item() and torch.isnan(am2).item()
+    else:
+        assert am1.item() == am2.item() == max(start, true_amax)
+    z = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)  # all-zero tensor from -1.0: both report 0
+    am1, am2 = torch.tensor([-1.0], device=DEV), torch.tensor([-1.0], device=DEV)
+    scaled_quant(z, scale, am1, torch.float8_e4m3fn, True)
+    scaled_quant_transpose(z, scale, am2, torch.float8_e4m3fn, True)
+    assert am1.item() == 0.0 and am2.item() == 0.0

@@ -97,3 +97,28 @@ def test_every_op_is_deterministic():
     assert len(first) == len(second)
     for a, b in zip(first, second):
         assert torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))
+
+
+def test_check_status_reports_and_repairs_the_workspace():
+    """What a kernel leaves behind when a bounded wait expires (status word set, a grid-barrier
+    counter not rewound) is written into the workspace from the host here - no wait is made to
+    expire.  check_status turns it into TnqError(ETIMEOUT), zeroes the header, and the single-launch
+    cast that uses those barrier words is bit-exact again afterwards."""
+    import oracle
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
+    x = make_input("fp8_tensor", DEV, rows=512, cols=512)
+    want, want_scale = oracle.fp8_dynamic_quant(x.cpu(), torch.float8_e4m3fn)
+    q, s = tn.dynamic_scaled_quant_with_scale(x)
+    _lib.check_status(x.device)  # clean
+    ws = _lib.workspace(x.device)
+    ws[_lib.WS_STATUS_WORD] = 6
+    ws[4] = 3  # bar_count as an abandoned grid barrier would leave it
+    with pytest.raises(_lib.TnqError) as e:
+        _lib.check_status(x.device, what="tnq_fp8_dynamic_cast")
+    assert e.value.status == 6
+    assert int(ws[:16].abs().sum().item()) == 0
+    q, s = tn.dynamic_scaled_quant_with_scale(x)
+    _lib.check_status(x.device)
+    assert torch.equal(q.view(torch.uint8).cpu(), want.view(torch.uint8)) and torch.equal(s.cpu(), want_scale)

@@ -51,6 +51,17 @@ def test_reference_saturation_case(golden, dname):
     assert am.item() == torch.finfo(DT[dname]).max + 100
 
 
+@pytest.mark.parametrize("dname", ["e4m3", "e5m2"])
+def test_rowwise_matches_reference_applied_per_row(golden, dname):
+    """The row-wise oracle against bytes and scales produced by the reference's
+    eager_scaled_quant called once per row (zero, outlier, NaN, -inf and subnormal rows)."""
+    g = golden("fp8_rowwise.npz")
+    x = bf16_from_bits(g["x_bits"])
+    q, s = oracle.fp8_rowwise_quant(x, DT[dname])
+    assert np.array_equal(as_u8(q).numpy(), g[f"q_{dname}"])
+    assert np.array_equal(s.numpy().view(np.uint32), g[f"scale_{dname}"].view(np.uint32))
+
+
 def test_mxfp8_ceil_matches_reference(golden):
     g = golden("mxfp8.npz")
     x = bf16_from_bits(g["x_bits"])

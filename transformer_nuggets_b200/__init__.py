@@ -16,6 +16,7 @@ from .mx.quantize import quantize_mxfp8  # noqa: F401
 from .cute.mxfp8_tma import quantize_mxfp8_tensor  # noqa: F401
 from .cute.nvfp4_tma import pack_nvfp4_codes, quantize_nvfp4, swizzle_nvfp4_scales  # noqa: F401
 from .cute.to_blocked import to_blocked_mx  # noqa: F401
+from ._lib import TnqError, check_status  # noqa: F401
 
 __all__ = [
     "scaled_quant",
@@ -29,4 +30,6 @@ __all__ = [
     "quantize_nvfp4",
     "pack_nvfp4_codes",
     "swizzle_nvfp4_scales",
+    "check_status",
+    "TnqError",
 ]

@@ -6,6 +6,7 @@ argument is not a CUDA tensor the call raises.
 
 from __future__ import annotations
 
+import collections
 import ctypes
 import os
 import threading
@@ -103,6 +104,11 @@ def load():
     return _lib
 
 
+#: ``TNQ_CHECK_STATUS=1`` in the environment makes every entry point synchronise and read the
+#: device status word after its launch (debugging aid; costs a device synchronisation per call).
+CHECK_EVERY_CALL = os.environ.get("TNQ_CHECK_STATUS", "0") not in ("", "0")
+
+
 def call(name, *args):
     lib = load()
     rc = getattr(lib, name)(*args)
@@ -111,6 +117,8 @@ def call(name, *args):
         if rc == 5:
             detail += f" (cudaError {lib.tnq_last_cuda_error()})"
         raise TnqError(name, rc, detail)
+    if CHECK_EVERY_CALL and name not in _NO_LAUNCH:
+        check_status(torch.cuda.current_device(), what=name)
 
 
 def stream_ptr(device) -> int:
@@ -121,14 +129,42 @@ def ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+#: compute capabilities the library image holds code for (built for sm_100a only)
+SUPPORTED_CAPABILITIES = {(10, 0)}
+_capability_ok: dict = {}
+
+
+def require_capability(index: int):
+    """Raise ``ValueError`` unless device ``index`` is a B200-class GPU.  The reference's CuTe
+    entry points refuse other parts the same way before any launch (cute/mxfp8_tma.py:275); here
+    the check also keeps a launch on another architecture from surfacing as a bare CUDA error."""
+    if _capability_ok.get(index):
+        return
+    cap = tuple(torch.cuda.get_device_capability(index))
+    if cap not in SUPPORTED_CAPABILITIES:
+        raise ValueError(
+            f"device {index} has compute capability {cap[0]}.{cap[1]}; these kernels are built for "
+            "sm_100a (compute capability 10.0) only"
+        )
+    _capability_ok[index] = True
+
+
 def require_cuda(t: torch.Tensor, what: str):
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{what} must be a torch.Tensor")
     if not t.is_cuda:
         raise ValueError(f"{what} must be a CUDA tensor: the cast kernels have no CPU path")
+    require_capability(t.device.index if t.device.index is not None else torch.cuda.current_device())
 
 
-_workspaces: dict = {}
+#: entry points that launch nothing (no status to look at afterwards)
+_NO_LAUNCH = {"tnq_set_option", "tnq_rowwise_set_tma", "tnq_rowwise_set_group", "tnq_exchange_create",
+              "tnq_exchange_open", "tnq_exchange_close", "tnq_exchange_destroy", "tnq_exchange_status"}
+
+#: most recently used (device, stream) -> workspace; bounded so that a program that keeps creating
+#: streams does not accumulate scratch tensors for streams that no longer exist
+MAX_WORKSPACES = 64
+_workspaces: "collections.OrderedDict" = collections.OrderedDict()
 
 
 def workspace(device) -> torch.Tensor:
@@ -140,4 +176,36 @@ def workspace(device) -> torch.Tensor:
     if ws is None:
         ws = torch.zeros(WORKSPACE_BYTES // 4, dtype=torch.int32, device=torch.device("cuda", idx))
         _workspaces[key] = ws
+        while len(_workspaces) > MAX_WORKSPACES:  # the evicted tensor returns to the allocator of its own stream
+            _workspaces.popitem(last=False)
+    else:
+        _workspaces.move_to_end(key)
     return ws
+
+
+def check_status(device=None, what: str = "a kernel"):
+    """Synchronise ``device`` and read the status word of every workspace this module handed out on
+    it.  The kernels never wait without a bound: a wait that gives up (a TMA copy, the grid barrier
+    of the single-launch cast, a peer's amax word) records ``TNQ_ETIMEOUT`` there and the kernel
+    returns, leaving its outputs incomplete.  This is the call that turns that record into an
+    exception.  It also puts the workspace header (the first 64 bytes: ticket, barrier counters,
+    status) back to zero, because a kernel that left early may not have rewound them.  Raises
+    ``TnqError`` with ``status == 6`` if any word was set."""
+    if device is None:
+        idx = torch.cuda.current_device()
+    else:
+        device = torch.device(device) if not isinstance(device, int) else torch.device("cuda", device)
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+    bad = None
+    for (dev_idx, _stream), ws in list(_workspaces.items()):
+        if dev_idx != idx:
+            continue
+        if ws.is_cuda:
+            torch.cuda.synchronize(idx)
+        st = int(ws[WS_STATUS_WORD].item())
+        if st != 0:
+            bad = st
+            ws[:16].zero_()
+    if bad is not None:
+        raise TnqError(what, bad, "(device status word: a bounded device-side wait expired; outputs of the "
+                                  "calls since the last check are incomplete)")

@@ -5,9 +5,12 @@
 // in registers between the amax reduction and the cast, so the input crosses HBM
 // once.  Groups of 32 reduce with warp shuffles only; larger groups add one shared
 // memory exchange.  The grid is persistent (resident CTAs only) and strides over
-// row groups.  The default kernel stages rows in shared memory with bulk async
-// copies (TMA) ahead of the consumers; a direct-load variant is kept for comparison.
+// row groups.  The default kernel loads rows straight into registers with 256-bit
+// global loads; a variant that stages rows in shared memory with bulk async copies
+// (TMA) ahead of the consumers is kept behind tnq_rowwise_set_tma (slower here).
 // Rows longer than 32 KiB take a two-pass kernel whose second read comes from L1/L2.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace tnq {
@@ -380,8 +383,8 @@ static int pick_vpt(int per_thread, const uint8_t* x, int64_t rows, int64_t cols
   return launch_rowwise<IN, G, 4>(x, rows, cols, nvec_row, q43, s43, q52, s52, stream);
 }
 
-static int g_rowwise_tma = 0;
-static int g_rowwise_group = 0;  // 0 = automatic, else force 32/64/128/256 threads per row where legal
+static std::atomic<int> g_rowwise_tma{0};
+static std::atomic<int> g_rowwise_group{0};  // 0 = automatic, else force 32/64/128/256 threads per row where legal
 extern "C" int tnq_rowwise_set_tma(int on) {
   g_rowwise_tma = on ? 1 : 0;
   return TNQ_OK;

@@ -7,6 +7,8 @@
 // unroll 1..8; 640- and 768-thread CTAs lose 7-12 %), |x| maxima on the integer view, one warp `redux` + one shared
 // memory step per CTA, and a self-resetting ticket so that the last CTA to finish
 // combines the per-CTA partial maxima (no float atomics, no memset between calls).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace tnq {
@@ -294,8 +296,11 @@ __global__ void __launch_bounds__(kThreads)
     if (grid_max(m, ws, smem32, &total)) {
       const float amax = __uint_as_float(total);
       ws->amax_bits = total;
-      const float old = *abs_max_inout;
-      if (!(old >= amax)) *abs_max_inout = amax;  // max(old, amax); a NaN amax wins
+      // max(old, amax) on the magnitude bits, like every other reduction here: a NaN on either
+      // side stays (a history word that was poisoned once is not silently repaired)
+      // signed compare of the bit patterns: a negative old value (callers start from -1.0) loses
+      const int32_t old = __float_as_int(*abs_max_inout);
+      if (old < (int32_t)total) *abs_max_inout = amax;
     }
   }
 }
@@ -347,27 +352,30 @@ static int stream_grid(int64_t n_vec) {
   return (int)(want < cap ? want : cap);
 }
 
-static int g_cast_reverse = 1;
-static int g_fused_small = 1;
-static int g_l2_keep_mb = 64;
-static int g_cast_l2_mode = 0;
+// tuning switches: read by any thread that launches, written by tnq_set_option (relaxed atomics:
+// a launch sees either the old or the new value, never a torn one)
+static std::atomic<int> g_cast_reverse{1};
+static std::atomic<int> g_fused_small{1};
+static std::atomic<int> g_l2_keep_mb{64};
+static std::atomic<int> g_cast_l2_mode{0};
 // Walking backwards only pays once the tensor no longer fits in L2 as a whole.
 constexpr int64_t kReverseMinBytes = 96ll << 20;
 
 // First vector of the tail that the amax pass asks L2 to keep for the cast pass.
 static int64_t keep_from_vec(int64_t n, int in_dtype) {
   const int64_t bytes = n * (in_dtype == TNQ_IN_BF16 ? 2 : 4), nvec = bytes / 32;
-  if (!g_cast_reverse || g_l2_keep_mb <= 0 || bytes <= kReverseMinBytes) return nvec;
-  const int64_t keep_vec = ((int64_t)g_l2_keep_mb << 20) / 32;
+  const int keep_mb = g_l2_keep_mb.load(std::memory_order_relaxed);
+  if (!g_cast_reverse.load(std::memory_order_relaxed) || keep_mb <= 0 || bytes <= kReverseMinBytes) return nvec;
+  const int64_t keep_vec = ((int64_t)keep_mb << 20) / 32;
   return keep_vec >= nvec ? 0 : nvec - keep_vec;
 }
 
 extern "C" int tnq_set_option(int option, int value) {
   switch (option) {
-    case TNQ_OPT_CAST_REVERSE: g_cast_reverse = value ? 1 : 0; return TNQ_OK;
-    case TNQ_OPT_FUSED_SMALL: g_fused_small = value ? 1 : 0; return TNQ_OK;
-    case TNQ_OPT_L2_KEEP_MB: g_l2_keep_mb = value < 0 ? 0 : value; return TNQ_OK;
-    case TNQ_OPT_CAST_L2_MODE: g_cast_l2_mode = value & 3; return TNQ_OK;
+    case TNQ_OPT_CAST_REVERSE: g_cast_reverse.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_FUSED_SMALL: g_fused_small.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_L2_KEEP_MB: g_l2_keep_mb.store(value < 0 ? 0 : value, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_CAST_L2_MODE: g_cast_l2_mode.store(value & 3, std::memory_order_relaxed); return TNQ_OK;
     default: return TNQ_EINVAL;
   }
 }
@@ -437,8 +445,8 @@ static int cast_any(const void* x, void* out, int64_t n, int in_dtype, int out_d
   // a cast that follows an amax pass over the same tensor may walk it backwards
   const int64_t in_bytes = n * (in_dtype == TNQ_IN_BF16 ? 2 : 4);
   const bool after_amax = pdl || scale_source == TNQ_SCALE_IS_AMAX;
-  const int reverse = (after_amax && g_cast_reverse && in_bytes > kReverseMinBytes) ? 1 : 0;
-  const int l2_mode = reverse ? g_cast_l2_mode : 0;
+  const int reverse = (after_amax && g_cast_reverse.load(std::memory_order_relaxed) && in_bytes > kReverseMinBytes) ? 1 : 0;
+  const int l2_mode = reverse ? g_cast_l2_mode.load(std::memory_order_relaxed) : 0;
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* op = static_cast<uint8_t*>(out);
   Workspace* ws = static_cast<Workspace*>(workspace);
@@ -471,7 +479,7 @@ extern "C" int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_
   if (rc != TNQ_OK) return rc;
   if (workspace == nullptr || (n > 0 && out == nullptr)) return TNQ_EINVAL;
   if (!aligned16(out)) return TNQ_EALIGN;
-  if (g_fused_small) {  // the whole tensor fits in shared memory: one launch, one HBM read
+  if (g_fused_small.load(std::memory_order_relaxed)) {  // the whole tensor fits in shared memory: one launch, one HBM read
     int grid = 0;
     uint32_t slab = 0;
     if (fused_plan(n * (in_dtype == TNQ_IN_BF16 ? 2 : 4), &grid, &slab))
@@ -575,7 +583,7 @@ extern "C" int tnq_fp8_dynamic_cast_static(const void* x, void* out, int64_t n, 
   cudaError_t e = cudaMemsetAsync(scratch, 0, 64, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   Workspace* ws = static_cast<Workspace*>(scratch);
-  rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream);
+  rc = amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, ws, nullptr, scale_out, fp8_max_of(out_dtype), stream, true);
   if (rc != TNQ_OK) return rc;
   return cast_any(x, out, n, in_dtype, out_dtype, &ws->scale, TNQ_SCALE_IS_SCALE, 1, nullptr, scratch, stream, true);
 }

@@ -153,12 +153,14 @@ __global__ void __launch_bounds__(512, 2)
     ahead.advance();
     if (++s == (uint32_t)kStages) s = 0, phase ^= 1u;
   }
-  // max|x| of everything the row group saw -> abs_max (integer-ordered: non-negative floats, NaN on top)
+  // max|x| of everything the row group saw -> abs_max.  Signed compare of the bit patterns:
+  // non-negative floats order like their bits with NaN on top, and a negative old value
+  // (callers start from -1.0) loses to any magnitude
   if (p.abs_max != nullptr && group == 0) {
     const uint32_t wm = warp_max_u32(fold_u16x2(m));
     if ((gtid & 31) == 0 && wm != 0u) atomicMax(cta_max, wm);
     named_barrier<1, 256>();
-    if (gtid == 0 && *cta_max != 0u) atomicMax(reinterpret_cast<uint32_t*>(p.abs_max), *cta_max << 16);
+    if (gtid == 0) atomicMax(reinterpret_cast<int*>(p.abs_max), (int)(*cta_max << 16));
   }
 }
 

@@ -38,3 +38,16 @@ def to_blocked_manual(input_matrix: Tensor) -> Tensor:
     """The reference's second implementation of the same rearrangement
     (mx/to_blocked.py:67-105) under its own name; one kernel serves both."""
     return to_blocked(input_matrix)
+
+
+def _to_blocked_single(scales: Tensor) -> Tensor:
+    """One 128 x 4 block of scales -> its ``(32, 16)`` atom (mx/to_blocked.py:56-65 of the
+    reference): a single-atom call of the same kernel."""
+    assert scales.shape == (128, 4)
+    return to_blocked(scales).view(32, 16)
+
+
+def _to_blocked_single_manual(scales: Tensor) -> Tensor:
+    """The reference's slow twin of ``_to_blocked_single`` (mx/to_blocked.py:45-53) under its
+    own name; one kernel serves both."""
+    return _to_blocked_single(scales.reshape(128, 4))
