@@ -31,6 +31,8 @@ if ROOT not in sys.path:
 METRIC = "quant_cast_hbm_bandwidth"
 UNIT = "GB/s"
 HEADLINE = "fp8_sharded"
+# the arithmetic type of the path: one fp32 product per element between the bf16 load and the fp8 cvt
+DTYPE = "f32 (bf16 in, e4m3 out)"
 
 
 def measured_peak_gbs():
@@ -40,6 +42,23 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def measured_traffic(kernel, elements):
+    """DRAM bytes one launch of `kernel` moves, from the counters of an ncu capture of a smaller launch
+    of the same kernel (the full-size launch holds too much memory for a multi-pass capture), scaled by
+    the element count: traffic of these streaming kernels is proportional to it.  The capture's figures
+    live in a small data file beside its summary."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)[kernel]
+        per_elem = (rec["dram_bytes_read"] + rec["dram_bytes_write"]) / rec["elements"]
+        return {"traffic": per_elem * elements, "traffic_bytes_per_element": per_elem,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one 16384 x 8192 launch "
+                                  "(profiles/dram_traffic.json), scaled by elements"}
+    except Exception:
+        return {"traffic": None, "traffic_source": "no capture on file"}
 
 
 # --------------------------------------------------------------------------- clocks
@@ -103,31 +122,70 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU reference arm
-def cpu_reference_pass(name, x):
-    """One pass of the reference's CPU (eager PyTorch) arithmetic for workload `name`,
-    through the oracle port.  Returns nothing; the caller times it."""
+CHUNK_ROWS = 4096  # the CPU passes walk the tensor in row chunks so that fp32 temporaries stay small
+
+
+def reference_functions():
+    """The reference's own Python functions from the unmodified copy under oracle/_ref, or
+    (None, reason) when that copy cannot be imported here."""
+    try:
+        from oracle import reference
+
+        sq = reference.load("fp8.scaled_quant")
+        mx = reference.load("cute.mxfp8_tma")
+        tb = reference.load("mx.to_blocked")
+        return {"eager_scaled_quant": sq.eager_scaled_quant, "quantize_mxfp8_tensor": mx.quantize_mxfp8_tensor,
+                "to_blocked": tb.to_blocked}, None
+    except Exception as e:  # noqa: BLE001 - any import problem means "fall back to the port and say why"
+        return None, f"{type(e).__name__}: {e}"[:200]
+
+
+def cpu_reference_pass(name, x, ref):
+    """One pass of the reference's CPU (eager PyTorch) path for workload `name` over all of `x`.
+    With `ref` (see reference_functions) the reference's own functions run; otherwise, and for the
+    two configurations the reference has no function for (row-wise, NVFP4), the oracle port.
+    Returns "reference" or "port"."""
     import torch
 
     import oracle
 
     if name in ("fp8_sharded", "fp8_tensor"):
-        oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)
-    elif name == "fp8_rowwise":
-        oracle.fp8_rowwise_quant(x, torch.float8_e4m3fn)
-        oracle.fp8_rowwise_quant(x, torch.float8_e5m2)
-    elif name == "mxfp8":
-        _, s = oracle.mxfp8_quantize(x, "ceil")
-        oracle.to_blocked(s)
-        _, s = oracle.mxfp8_quantize(x.t().contiguous(), "ceil")
-        oracle.to_blocked(s)
-    elif name == "nvfp4":
-        _, s, _ = oracle.nvfp4_quantize(x)
-        oracle.to_blocked(s.view(torch.uint8))
-    else:
-        raise KeyError(name)
+        # dynamic per-tensor cast = amax pass, then fp8/scaled_quant.py:78-102 with scale = 448 / amax, saturated
+        amax = torch.zeros((), dtype=torch.float32)
+        for r0 in range(0, x.shape[0], CHUNK_ROWS):
+            amax = torch.maximum(amax, x[r0:r0 + CHUNK_ROWS].abs().max().float())
+        scale = (torch.tensor(448.0) / amax.clamp(min=1e-12)).reshape(1)
+        am = torch.zeros(1)
+        fn = ref["eager_scaled_quant"] if ref else oracle.fp8_scaled_quant
+        for r0 in range(0, x.shape[0], CHUNK_ROWS):
+            fn(x[r0:r0 + CHUNK_ROWS], scale, am, torch.float8_e4m3fn, True)
+        return "reference" if ref else "port"
+    if name == "fp8_rowwise":
+        for r0 in range(0, x.shape[0], CHUNK_ROWS):
+            oracle.fp8_rowwise_quant(x[r0:r0 + CHUNK_ROWS], torch.float8_e4m3fn)
+            oracle.fp8_rowwise_quant(x[r0:r0 + CHUNK_ROWS], torch.float8_e5m2)
+        return "port"
+    if name == "mxfp8":
+        quant = ref["quantize_mxfp8_tensor"] if ref else (lambda v: oracle.mxfp8_quantize(v, "ceil"))
+        blocked = ref["to_blocked"] if ref else oracle.to_blocked
+        _, s = quant(x)
+        blocked(s)
+        _, s = quant(x.t().contiguous())
+        blocked(s)
+        return "reference" if ref else "port"
+    if name == "nvfp4":
+        amax = x.abs().max().float()
+        for r0 in range(0, x.shape[0], CHUNK_ROWS):
+            _, s, _ = oracle.nvfp4_quantize(x[r0:r0 + CHUNK_ROWS], amax)
+            oracle.to_blocked(s.view(torch.uint8))
+        return "port"
+    raise KeyError(name)
 
 
-def cpu_baseline(name, steps, warmup, sample_rows):
+def cpu_baseline(name, steps, warmup, sample_rows, budget_s=None):
+    """Time the CPU path on the first `sample_rows` rows of workload `name` with every host thread.
+    `budget_s`: shrink the sample (and say so) if warm-up shows that steps + warmup passes would
+    take longer than that."""
     import torch
 
     from transformer_nuggets_b200.workloads import CONFIGS, make_input
@@ -137,23 +195,34 @@ def cpu_baseline(name, steps, warmup, sample_rows):
         torch.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1
     except Exception:
         pass
+    ref, why = reference_functions()
     x = make_input(name, "cpu", rows=sample_rows)
-    for _ in range(warmup):
-        cpu_reference_pass(name, x)
+    t = time.perf_counter()
+    kind = cpu_reference_pass(name, x, ref)
+    first = time.perf_counter() - t
+    if budget_s is not None and first * (steps + warmup) > budget_s and sample_rows > 1024:
+        keep = max(1024, int(sample_rows * budget_s / (first * (steps + warmup))) // 1024 * 1024)
+        x = x[:keep].contiguous()
+        sample_rows = keep
+    for _ in range(max(warmup - 1, 0)):
+        cpu_reference_pass(name, x, ref)
     times = []
     for _ in range(steps):
         t = time.perf_counter()
-        cpu_reference_pass(name, x)
+        cpu_reference_pass(name, x, ref)
         times.append(time.perf_counter() - t)
     sec = sum(times) / len(times)
     nbytes = cfg.algo_bytes_per_elem * x.numel()
+    what = {"reference": "the reference's own functions (unmodified copy under oracle/_ref)",
+            "port": "the oracle port of the reference path" + (f" (reference copy not importable: {why})" if why else
+                                                                " (the reference has no function for this configuration)")}[kind]
     return {
         "value": nbytes / sec / 1e9,
         "unit": UNIT,
         "cores": torch.get_num_threads(),
-        "kind": "port",
+        "kind": kind,
         "sample": f"{sample_rows} of {cfg.rows} rows x {cfg.cols} cols ({name}), {steps} timed passes, "
-                  f"{sec * 1e3:.1f} ms per pass, PyTorch CPU eager ops of the reference path",
+                  f"{sec * 1e3:.1f} ms per pass, PyTorch CPU eager ops: {what}",
     }, sec
 
 
@@ -161,21 +230,154 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload == "comparators":
+        emit(run_comparators())
+        return
     from transformer_nuggets_b200.workloads import CONFIGS
 
     cfg = CONFIGS[args.workload]
-    sample_rows = max(128, cfg.rows // 32)
-    base, sec = cpu_baseline(args.workload, args.steps, args.warmup, sample_rows)
+    # the whole configuration when the host gets through steps + warmup passes of it in ~2.5 minutes
+    base, sec = cpu_baseline(args.workload, args.steps, args.warmup, cfg.rows, budget_s=150.0)
     line = {
         "impl": "reference",
         "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
         "config": workload_config(args.workload, args.gpus, "none (CPU)"),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     emit(line)
+
+
+def run_comparators():
+    """`--impl reference --workload comparators`: the reference's own GPU code on this machine, from the
+    unmodified copy under oracle/_ref, timed with CUDA events on cuda:0 like this library's kernels
+    (none of this library's kernels run in this process).  Each entry is {"us": ...} or
+    {"unavailable": reason}.  The reference's Triton `dynamic_scaled_quant` is never run: its grid-wide
+    spin lock is on record as hanging above 2^22 elements (benchmarks/fp8_dynamic_cast.py:43-45 there)."""
+    import torch
+
+    out = {"impl": "reference", "what": "reference GPU code on the same machine (oracle/_ref), CUDA events, cuda:0"}
+    try:
+        from oracle import reference
+
+        sq = reference.load("fp8.scaled_quant")
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"{type(e).__name__}: {e}"[:300]
+        return out
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+
+    def timed(fn, iters=20, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    def attempt(name, build):
+        """build() -> (callable, elements or None, algorithmic bytes); guarded: a comparator that does not
+        import, compile or launch here is reported, not fatal."""
+        try:
+            fn, nbytes, note = build()
+            us = timed(fn)
+            out[name] = {"us": us, "GBps": nbytes / (us * 1e-6) / 1e9, "note": note}
+        except Exception as e:  # noqa: BLE001
+            out[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+
+    g = torch.Generator(device=dev).manual_seed(77)
+
+    def eager_dynamic(rows, cols):
+        def build():
+            x = torch.randn(rows, cols, device=dev, generator=g).to(torch.bfloat16)
+            am = torch.zeros(1, device=dev)
+
+            def fn():  # amax -> scale -> the reference's eager cast, as the dynamic cast's eager twin does
+                scale = (448.0 / x.abs().max().float().clamp(min=1e-12)).reshape(1)
+                sq.eager_scaled_quant(x, scale, am, torch.float8_e4m3fn, True)
+
+            bpe = 3.0 if rows * cols * 2 <= (64 << 20) else 5.0
+            return fn, bpe * rows * cols, f"eager_scaled_quant on CUDA tensors behind an eager amax, bf16 {rows}x{cols}"
+        return build
+
+    attempt("eager_dynamic_cast_4096x4096", eager_dynamic(4096, 4096))
+    attempt("eager_dynamic_cast_16384x8192", eager_dynamic(16384, 8192))
+
+    def triton_delayed(dtype):
+        def build():
+            rows, cols = 16384, 8192
+            x = torch.randn(rows, cols, device=dev, generator=g).to(dtype)
+            scale = torch.full((1,), 0.5, device=dev)
+            am = torch.zeros(1, device=dev)
+
+            def fn():
+                sq.scaled_quant(x, scale, am, torch.float8_e4m3fn, True)
+
+            return fn, (x.element_size() + 1.0) * rows * cols, f"Triton scaled_quant (delayed scale + abs_max), {dtype} {rows}x{cols}"
+        return build
+
+    attempt("triton_delayed_cast_bf16_16384x8192", triton_delayed(torch.bfloat16))
+    attempt("triton_delayed_cast_f32_16384x8192", triton_delayed(torch.float32))
+
+    def eager_mxfp8():
+        mx = reference.load("cute.mxfp8_tma")
+        tb = reference.load("mx.to_blocked")
+        rows, cols = 8192, 7168
+        x = torch.randn(rows, cols, device=dev, generator=g).to(torch.bfloat16)
+
+        def fn():
+            _, s = mx.quantize_mxfp8_tensor(x)
+            tb.to_blocked(s)
+            _, s = mx.quantize_mxfp8_tensor(x.t().contiguous())
+            tb.to_blocked(s)
+
+        return fn, 4.0625 * rows * cols, "quantize_mxfp8_tensor + to_blocked on x and x^T (eager CUDA ops), bf16 8192x7168"
+
+    attempt("eager_mxfp8_row_col_8192x7168", eager_mxfp8)
+
+    def gemv_mxfp8():
+        mx = reference.load("cute.mxfp8_tma")
+        tb = reference.load("mx.to_blocked")
+        bs = reference.load("cute.blockscaled_tma")
+        n, k = 32768, 8192
+        w = torch.randint(0, 0x7E, (n, k), device=dev, dtype=torch.uint8, generator=g).view(torch.float8_e4m3fn)
+        xq = torch.randint(0, 0x7E, (1, k), device=dev, dtype=torch.uint8, generator=g).view(torch.float8_e4m3fn)
+        ws = tb.to_blocked(torch.randint(120, 134, (n, k // 32), device=dev, dtype=torch.uint8, generator=g))
+        xs = tb.to_blocked(torch.randint(120, 134, (1, k // 32), device=dev, dtype=torch.uint8, generator=g))
+        y = torch.empty(1, n, dtype=torch.bfloat16, device=dev)
+
+        def fn():  # block_n / stages / warps: the reference benchmark's B200 choice for K = 8192
+            mx.mxfp8_tma_gemv(xq, w, xs, ws, block_n=4, num_stages=2, output=y, num_compute_warps=4,
+                              grid_scheduler=bs.GridScheduler.STATIC, block_scale_layout=bs.BlockScaleLayout.SWIZZLE_32_4_4)
+
+        return fn, n * k * (1 + 1 / 32) + k * (1 + 1 / 32) + 2 * n, f"mxfp8_tma_gemv (CuTe DSL), N={n} K={k}, swizzled scales"
+
+    attempt("gemv_mxfp8_32768x8192", gemv_mxfp8)
+
+    def gemv_nvfp4():
+        nv = reference.load("cute.nvfp4_tma")
+        n, k = 32768, 16384
+        w = torch.randint(0, 256, (n, k // 2), device=dev, dtype=torch.uint8, generator=g).view(torch.float4_e2m1fn_x2)
+        xq = torch.randint(0, 256, (1, k // 2), device=dev, dtype=torch.uint8, generator=g).view(torch.float4_e2m1fn_x2)
+        ws = nv.swizzle_nvfp4_scales(torch.randint(0x30, 0x40, (n, k // 16), device=dev, dtype=torch.uint8, generator=g).view(torch.float8_e4m3fn))
+        xs = nv.swizzle_nvfp4_scales(torch.randint(0x30, 0x40, (1, k // 16), device=dev, dtype=torch.uint8, generator=g).view(torch.float8_e4m3fn))
+        gs = torch.full((1,), 0.5, device=dev)
+        y = torch.empty(1, n, dtype=torch.bfloat16, device=dev)
+
+        def fn():  # block_n=None: the reference's own B200 selector
+            nv.nvfp4_tma_gemv(xq, w, xs, ws, input_global_scale=gs, weight_global_scale=gs, output=y)
+
+        return fn, n * k * (0.5 + 1 / 16) + k * (0.5 + 1 / 16) + 2 * n, f"nvfp4_tma_gemv (CuTe DSL), N={n} K={k}, global scales"
+
+    attempt("gemv_nvfp4_32768x16384", gemv_nvfp4)
+    return out
 
 
 def workload_config(name, n_gpus, exchange, rows=None):
@@ -214,6 +416,32 @@ def bind_near_gpu(index):
         return f"bound to {len(use)} GPU-local CPUs"
     except Exception as e:  # NVML missing or affinity not permitted
         return f"unchanged ({type(e).__name__})"
+
+
+def headline_parity(x, got, amax_dev, rank, world, dist, dev):
+    """Every rank checks 2048 of its rows (a seeded contiguous block) of the sharded cast against
+    oracle.fp8_scaled_quant fed the scale of the whole tensor, and the exchanged amax against a plain
+    torch reduction of its own rows MAX-reduced over the ranks.  Returns the record for the JSON line
+    (ok = every rank agreed on every byte)."""
+    import torch
+
+    import oracle
+
+    local = x.abs().max().float().reshape(1)
+    if dist is not None:
+        dist.all_reduce(local, op=dist.ReduceOp.MAX)
+    amax_ok = bool(torch.equal(local, amax_dev.reshape(1)))
+    scale = (torch.tensor([448.0]) / local.cpu().clamp(min=1e-12)).reshape(1)
+    n = min(2048, x.shape[0])
+    g = torch.Generator().manual_seed(4242 + rank)
+    r0 = int(torch.randint(0, x.shape[0] - n + 1, (1,), generator=g))
+    want = oracle.fp8_scaled_quant(x[r0:r0 + n].cpu(), scale, torch.zeros(1), torch.float8_e4m3fn, True)
+    rows_ok = bool(torch.equal(got[r0:r0 + n].view(torch.uint8).cpu(), want.view(torch.uint8)))
+    flag = torch.tensor([1 if (amax_ok and rows_ok) else 0], dtype=torch.int32, device=dev)
+    if dist is not None:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return {"ok": bool(flag.item()), "rows_checked": n * world, "ranks": world,
+            "against": "oracle.fp8_scaled_quant, 2048 seeded rows per rank, scale from the tensor-wide amax"}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -344,17 +572,13 @@ def run_ours(args):
         "other_kernels": {"k_amax": {"achieved": amax_gbs, "frac": amax_gbs / peak, "launch_ms": amax_ms,
                                      "algorithmic_bytes_per_launch": amax_bytes}},
     }
-    # DRAM traffic of k_cast from the ncu capture summarised in
-    # profiles/k_cast_k_amax_fp8_sharded_16384rows.md: 268.47 MB read + 87.77 MB written for
-    # 134 217 728 elements = 2.654 B/element (traffic is proportional to the element count; the
-    # 2 GiB case is too large for a multi-pass capture).
-    roofline["traffic"] = 2.654 * n_local
-    roofline["traffic_source"] = "ncu dram__bytes_read+write of a 16384x8192 launch, scaled by elements"
+    roofline.update(measured_traffic("k_cast", n_local))
 
     # ---- end to end: pinned host buffers in, pinned host buffers out, every step ----
     from transformer_nuggets_b200.dist.host_pipeline import HostCastPipeline
 
-    ref_out, _ = sharded_dynamic_scaled_quant(x, None, exchange=exchange)  # device-resident result to compare with
+    ref_out, amax_of_run = sharded_dynamic_scaled_quant(x, None, exchange=exchange)  # device-resident result to compare with
+    amax_of_run = amax_of_run.clone()
     all_cpus = os.sched_getaffinity(0)
     numa = bind_near_gpu(local_rank)  # pinned buffers are first touched from the GPU's own NUMA node
     host_in = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
@@ -378,15 +602,35 @@ def run_ours(args):
     barrier()
     e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
     ok_e2e = torch.equal(host_out[(args.steps - 1) % 2].view(torch.uint8), ref_out.view(torch.uint8).cpu())
+
+    # ---- the same copies alone: what the host link gives this many ranks at once (no kernels) ----
+    for i in range(2):
+        pipe.copy_only(host_in, host_out[i % 2])
+    pipe.synchronize()
+    barrier()
+    ev0.record()
+    pipe.s_h2d.wait_event(ev0)
+    for i in range(args.steps):
+        pipe.copy_only(host_in, host_out[i % 2])
+    torch.cuda.current_stream().wait_stream(pipe.s_d2h)
+    torch.cuda.current_stream().wait_stream(pipe.s_h2d)
+    ev1.record()
+    pipe.synchronize()
+    barrier()
+    copy_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+
+    # ---- parity of this rank's rows against the CPU oracle fed the tensor-wide amax ----
+    parity = headline_parity(x, ref_out, amax_of_run, rank, world, dist if world > 1 else None, dev)
     e2e = {
         "value": cfg.algo_bytes_per_elem * total_elems / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
         "ms_per_step": e2e_ms, "h2d_bytes_per_step": x.numel() * x.element_size(), "d2h_bytes_per_step": out.numel(),
-        "api": "transformer_nuggets_b200.dist.host_pipeline.HostCastPipeline.submit(pinned host rows -> pinned host fp8); "
-               "copies of consecutive steps overlap on separate streams",
+        "api": "HostCastPipeline.submit(pinned host rows -> pinned host fp8), copies of consecutive steps overlapped",
         "result_matches_device_path": bool(ok_e2e), "host_numa_binding": numa,
+        "copy_only_ms_per_step": copy_ms,
+        "copy_ceiling_gbs": cfg.algo_bytes_per_elem * total_elems / (copy_ms * 1e-3) / 1e9,
+        "frac_of_copy_ceiling": copy_ms / e2e_ms,
+        "h2d_gbs_per_gpu_in_copy_only": x.numel() * x.element_size() / (copy_ms * 1e-3) / 1e9,
     }
-    launches += 0  # the e2e and per-kernel passes are outside the timed region
-
     extras = None
     if world == 1 and not args.no_extras:
         extras = other_workloads(dev, peak)
@@ -394,31 +638,93 @@ def run_ours(args):
     base = None
     if rank == 0 and world == 1 and not args.no_cpu:
         base, _ = cpu_baseline(HEADLINE, 3, 1, cfg.rows // 8)
-        if extras is not None:  # the oracle port beside every other configuration, on a bounded row sample
+        if extras is not None:  # the CPU path beside every other configuration, on a bounded row sample
             for name, rows in (("fp8_tensor", 4096), ("fp8_rowwise", 2048), ("mxfp8", 1024), ("nvfp4", 512)):
                 if name in extras:
                     b, _ = cpu_baseline(name, 2, 1, rows)
-                    extras[name]["cpu_port"] = {"GBps": b["value"], "cores": b["cores"], "sample": b["sample"]}
+                    extras[name]["cpu"] = {"GBps": b["value"], "cores": b["cores"], "kind": b["kind"], "sample": b["sample"]}
+
+    comparators = None
+    if rank == 0 and world == 1 and not args.no_comparators:
+        comparators = run_comparators_in_child()
 
     if exchange is not None:
         exchange.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not parity["ok"]:
+        if rank == 0:
+            print(f"PARITY FAILURE: {parity}", file=sys.stderr)
+        raise SystemExit(3)
     if rank != 0:
         return
+
+    def compact(r):  # one configuration -> the four numbers of the grading contract
+        c = {"us": round(r["us"], 2), "GBps": round(r["GBps"], 1), "frac": round(r["frac_of_measured_peak"], 4),
+             "frac_nominal": round(r["frac_of_nominal_8000"], 4)}
+        if "parity" in r:
+            c["parity"] = r["parity"]
+        if "cpu" in r:
+            c["cpu_GBps"] = round(r["cpu"]["GBps"], 2)
+            c["cpu_kind"] = r["cpu"]["kind"]
+        return c
+
+    configs = {}
+    if extras is not None:
+        for key, name in (("cfg1_fp8_tensor_4096x4096", "fp8_tensor"), ("cfg2_fp8_rowwise_16384x8192", "fp8_rowwise"),
+                          ("cfg3_mxfp8_row_col_8192x7168", "mxfp8"), ("cfg4_nvfp4_16384x16384", "nvfp4")):
+            if name in extras:
+                configs[key] = compact(extras[name])
+    configs[f"cfg5_fp8_sharded_131072x8192_x{world}gpu"] = {
+        "us": round(ms_step * 1e3, 2), "GBps": round(value, 1), "frac": round(value / world / peak, 4),
+        "frac_nominal": round(value / world / 8000.0, 4), "parity": parity["ok"]}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": workload_config(HEADLINE, world, exchange_name, cfg.rows),
-        "frac_of_measured_peak_per_gpu": value / world / peak, "frac_of_nominal_8000_per_gpu": value / world / 8000.0,
+        "dtype": DTYPE, "data": "synthetic", "config": workload_config(HEADLINE, world, exchange_name, cfg.rows),
+        "configs": configs, "parity": parity,
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
     }
     if base is not None:
         line["cpu_baseline"] = base
     if extras is not None:
-        line["other_workloads"] = extras
+        line["next_rows"] = {k: ({kk: (round(vv, 4) if isinstance(vv, float) else vv) for kk, vv in v.items()
+                                  if kk not in ("note", "per_launch_us", "cpu", "parity_note")} if isinstance(v, dict) else v)
+                             for k, v in extras.items() if k not in ("fp8_tensor", "fp8_rowwise", "mxfp8", "nvfp4")}
+    if comparators is not None:
+        line["reference_same_box"] = comparators
+    line["frac_of_measured_peak_by_config"] = {k.split("_")[0]: v["frac"] for k, v in configs.items()}
+    if args.details:
+        with open(args.details, "w") as f:
+            json.dump({"line": line, "single_gpu_workloads": extras}, f, indent=1)
     emit(line)
+
+
+def run_comparators_in_child():
+    """The reference's GPU code, timed in a process of its own (`--impl reference --workload
+    comparators`): this process never imports it, and a comparator that misbehaves cannot take the
+    benchmark down with it.  Returns the child's record, or why there is none."""
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", "comparators"],
+                           capture_output=True, text=True, timeout=420,
+                           env={k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")})
+        for ln in reversed(r.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                rec = json.loads(ln)
+                rec.pop("impl", None)
+                for v in rec.values():
+                    if isinstance(v, dict):
+                        v.pop("note", None)
+                        if "unavailable" in v:
+                            v["unavailable"] = " ".join(v["unavailable"].encode("ascii", "ignore").decode().split())[:160]
+                        for k in ("us", "GBps"):
+                            if k in v:
+                                v[k] = round(v[k], 2)
+                return rec
+        return {"unavailable": f"no record from the child process (exit {r.returncode}): {r.stderr.strip()[-200:]}"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
 def other_workloads(dev, peak, only=None, iters=None, warm=None):
@@ -466,6 +772,11 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
 
     ws = _lib.workspace(dev)
     stream = _lib.stream_ptr(dev)
+    # A/B switches of the row + column kernels (same bytes either way; see include/tnq.h)
+    if os.environ.get("TNQ_MX_STORE_VARIANT"):
+        _lib.call("tnq_mxfp8_set_store_variant", int(os.environ["TNQ_MX_STORE_VARIANT"]))
+    if os.environ.get("TNQ_CT_STORE_VARIANT"):
+        _lib.call("tnq_cast_transpose_set_store_variant", int(os.environ["TNQ_CT_STORE_VARIANT"]))
 
     def report(name, ms, note, bytes_per_elem=None):
         cfg = CONFIGS[name]
@@ -492,14 +803,16 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _bench_transpose(dev, res, timed, peak, ws, stream)
     if want("rmsnorm_fp8"):
         _bench_rmsnorm(dev, res, timed, peak, stream)
-    if only == "fp8_gemm":  # tensor-core row; not part of the default run (a seconds-long dense GEMM loop)
-        _bench_fp8_gemm(dev, res, timed, stream)
+    if want("fp8_delayed"):
+        _bench_delayed(dev, res, timed, peak, ws, stream)
     if only == "mxfp8_gemm":
         _bench_mxfp8_gemm(dev, res, timed, stream)
     if only == "nvfp4_gemm":
         _bench_nvfp4_gemm(dev, res, timed, stream)
     if want("gemv") or only in ("gemv_mxfp8", "gemv_nvfp4"):
         _bench_gemv(dev, res, timed, peak, stream, None if only in (None, "gemv") else only)
+    if want("fp8_gemm"):  # tensor-core row, last: a dense GEMM loop runs the board into its power cap, and whatever
+        _bench_fp8_gemm(dev, res, timed, stream)  # is timed right behind it inherits the lowered clocks
     st = int(ws[_lib.WS_STATUS_WORD].item())
     if st != 0:
         raise SystemExit(f"device status word {st}: a bounded wait expired in a tile kernel")
@@ -546,6 +859,35 @@ def _bench_transpose(dev, res, timed, peak, ws, stream):
     res["fp8_dynamic_cast_transpose"] = report(timed(dynamic, [None]), 6.0,
                                                f"{rows}x{cols}, amax pass + transposing cast, input 256 MiB > L2")
     del x, q, q_t
+
+
+def _bench_delayed(dev, res, timed, peak, ws, stream):
+    """Delayed-scale saturated e4m3 cast with the abs_max side output (`scaled_quant`), 16384 x 8192, bf16 and
+    fp32 input: one read, one write (3 and 5 bytes per element).  The reference's Triton kernel for the same
+    call is timed on the same machine by the comparator run."""
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+    from transformer_nuggets_b200.workloads import make_input
+
+    xb = make_input("fp8_rowwise", dev)
+    rows, cols = xb.shape
+    q = torch.empty_like(xb, dtype=torch.float8_e4m3fn)
+    scale = torch.full((1,), 0.5, dtype=torch.float32, device=dev)
+    am = torch.zeros(1, dtype=torch.float32, device=dev)
+    for name, x, code, bpe in (("fp8_delayed_cast_bf16", xb, _lib.IN_BF16, 3.0), ("fp8_delayed_cast_f32", None, _lib.IN_F32, 5.0)):
+        if x is None:
+            x = xb.float()
+
+        def f(_):
+            _lib.call("tnq_fp8_scaled_cast", x.data_ptr(), q.data_ptr(), x.numel(), code, _lib.FP8_E4M3, scale.data_ptr(),
+                      _lib.SCALE_IS_SCALE, 1, am.data_ptr(), ws.data_ptr(), stream)
+
+        ms = timed(f, [None])
+        gbs = bpe * rows * cols / (ms * 1e-3) / 1e9
+        res[name] = {"us": ms * 1e3, "GBps": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+                     "algorithmic_bytes_per_element": bpe, "note": f"{rows}x{cols}, delayed scale, saturated, abs_max side output"}
+    del xb, q
 
 
 def _bench_rmsnorm(dev, res, timed, peak, stream):
@@ -639,8 +981,8 @@ def _bench_fp8_gemm(dev, res, timed, stream):
     except OSError:
         pass
     bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
-    ms = timed(ours, [None])
-    ms_lib = timed(library, [None])
+    ms = timed(ours, [None], 20, 5)
+    ms_lib = timed(library, [None], 20, 5)
     res["fp8_gemm"] = {
         "us": ms * 1e3, "TFLOPs": flops / (ms * 1e-3) / 1e12, "library_us": ms_lib * 1e3,
         "library_TFLOPs": flops / (ms_lib * 1e-3) / 1e12, "frac_of_library": ms_lib / ms,
@@ -800,7 +1142,13 @@ def _bench_fp8_tensor(dev, res, timed, report, ws, stream):
                   ws.data_ptr(), 0, stream)
 
     res["fp8_tensor"] = report("fp8_tensor", timed(f1, sets, 64, 16), "cold L2: 8 rotating buffer sets")
+    import oracle
+
+    want, _ = oracle.fp8_dynamic_quant(base.cpu(), torch.float8_e4m3fn)
+    res["fp8_tensor"]["parity"] = bool(torch.equal(sets[0][1].view(torch.uint8).cpu(), want.view(torch.uint8)))
     res["fp8_tensor_hot_l2"] = report("fp8_tensor", timed(f1, sets[:1], 64, 16), "hot L2: one buffer set")
+
+    res["fp8_tensor_phases"] = _fused_phases(dev, sets, ws, stream, res["fp8_tensor"]["us"])
 
     # the same eight calls replayed from one CUDA graph (launch overhead out of the picture)
     side = torch.cuda.Stream()
@@ -833,6 +1181,60 @@ def _bench_fp8_tensor(dev, res, timed, report, ws, stream):
     del sets, graph
 
 
+def _fused_phases(dev, sets, ws, stream, event_us):
+    """Where the single-launch cast's time goes: the kernel built with time stamps (at entry / slab loaded
+    and CTA maximum known / grid-wide exchange done / last store issued), cold L2 by the same rotating
+    buffer sets.  Per-CTA phase lengths from the SM clock (averaged over CTAs and launches, converted with
+    the SM clock NVML reports during the run) and, from the global timer, the launch's timeline measured
+    from the first CTA's start."""
+    import ctypes
+
+    import torch
+
+    from transformer_nuggets_b200 import _lib
+
+    stamps = torch.zeros(256 * 8, dtype=torch.int64, device=dev)
+    grid = ctypes.c_int(0)
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(dev.index or 0)
+    except Exception:
+        h = None
+
+    def run(s):
+        _lib.call("tnq_fp8_dynamic_cast_profile", s[0].data_ptr(), s[1].data_ptr(), s[0].numel(), ws.data_ptr(), 0,
+                  stamps.data_ptr(), ctypes.byref(grid), stream)
+
+    for it in range(16):
+        run(sets[it % len(sets)])
+    torch.cuda.synchronize()
+    mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)) if h is not None else None
+    acc, n = [0.0] * 7, 0
+    for it in range(16):
+        run(sets[it % len(sets)])
+        torch.cuda.synchronize()
+        t = stamps[: grid.value * 8].view(grid.value, 8).cpu().double()
+        first = t[:, 4].min()
+        acc[0] += float((t[:, 1] - t[:, 0]).mean())
+        acc[1] += float((t[:, 2] - t[:, 1]).mean())
+        acc[2] += float((t[:, 3] - t[:, 2]).mean())
+        acc[3] += float(t[:, 4].max() - first)
+        acc[4] += float((t[:, 5] - first).max())
+        acc[5] += float((t[:, 6] - first).max())
+        acc[6] += float((t[:, 7] - first).max())
+        n += 1
+    r = {"ctas": grid.value, "launches": n, "sm_mhz": mhz, "event_us_per_call": event_us,
+         "timeline_us_from_first_cta_start": {"last_cta_start": acc[3] / n / 1e3, "last_load_done": acc[4] / n / 1e3,
+                                              "exchange_done": acc[5] / n / 1e3, "last_exit": acc[6] / n / 1e3}}
+    r["between_kernels_us"] = event_us - r["timeline_us_from_first_cta_start"]["last_exit"]
+    if mhz:
+        r["mean_per_cta_us"] = {"load_and_cta_amax": acc[0] / n / mhz, "grid_exchange": acc[1] / n / mhz,
+                                "convert_and_store": acc[2] / n / mhz}
+    return r
+
+
 def _bench_rowwise(dev, res, timed, report, stream):
     import torch
 
@@ -849,6 +1251,15 @@ def _bench_rowwise(dev, res, timed, report, stream):
                   q52.data_ptr(), s52.data_ptr(), 0, stream)
 
     res["fp8_rowwise"] = report("fp8_rowwise", timed(f2, [None]), "input 256 MiB > L2")
+    import oracle
+
+    xs = x[4096:5120].cpu()
+    w43, ws43 = oracle.fp8_rowwise_quant(xs, torch.float8_e4m3fn)
+    w52, ws52 = oracle.fp8_rowwise_quant(xs, torch.float8_e5m2)
+    res["fp8_rowwise"]["parity"] = bool(
+        torch.equal(q43[4096:5120].view(torch.uint8).cpu(), w43.view(torch.uint8))
+        and torch.equal(q52[4096:5120].view(torch.uint8).cpu(), w52.view(torch.uint8))
+        and torch.equal(s43[4096:5120].cpu(), ws43) and torch.equal(s52[4096:5120].cpu(), ws52))
     del x, q43, q52
 
 
@@ -876,6 +1287,15 @@ def _bench_mxfp8(dev, res, timed, report, ws, stream):
 
     # input 112 MiB + outputs 114 MiB per call: rotate nothing, the footprint alone exceeds L2
     res["mxfp8"] = report("mxfp8", timed(f3, [None]), "row + column outputs, swizzled scales; footprint 226 MiB > L2")
+    import oracle
+
+    xc = x.cpu()
+    wq, wsr = oracle.mxfp8_quantize(xc[:1024], "ceil")  # 1024 rows of x, 1024 rows of x^T, and the scale atoms they own
+    wqt, wsc = oracle.mxfp8_quantize(xc[:, :1024].t().contiguous(), "ceil")
+    n_row, n_col = oracle.to_blocked(wsr).numel(), oracle.to_blocked(wsc).numel()
+    res["mxfp8"]["parity"] = bool(
+        torch.equal(qr[:1024].cpu(), wq.view(torch.uint8)) and torch.equal(qc[:1024].cpu(), wqt.view(torch.uint8))
+        and torch.equal(sr[:n_row].cpu(), oracle.to_blocked(wsr)) and torch.equal(sc[:n_col].cpu(), oracle.to_blocked(wsc)))
     res["mxfp8_rowwise_only"] = report("mxfp8", timed(f3r, [None]), "row-wise output only", 2.0 + 1.0 + 1.0 / 32)
     del x, qr, qc
 
@@ -904,6 +1324,14 @@ def _bench_nvfp4(dev, res, timed, report, ws, stream):
                   _lib.SCALES_SWIZZLED, gs.data_ptr(), status, stream)
 
     res["nvfp4"] = report("nvfp4", timed(f4, [None], 20, 4), "dynamic global scale (amax pass + quantize pass)")
+    import oracle
+
+    wp, wsf, wg = oracle.nvfp4_quantize(x[:512].cpu(), x.abs().max().float().cpu())
+    n_sf = oracle.to_blocked(wsf.view(torch.uint8)).numel()
+    res["nvfp4"]["parity"] = bool(
+        torch.equal(packed[:512].cpu(), wp.view(torch.uint8)) and torch.equal(gs.cpu(), wg.reshape(1))
+        and torch.equal(sf[:n_sf].cpu(), oracle.to_blocked(wsf.view(torch.uint8))))
+    res["nvfp4"]["parity_note"] = "against this build's own NVFP4 specification: the reference has no NVFP4 quantizer (unpinned)"
     res["nvfp4_given_global_amax"] = report("nvfp4", timed(f4s, [None], 20, 4), "global amax supplied", 2.5625)
 
 
@@ -930,6 +1358,8 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other single-GPU configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-comparators", action="store_true", help="skip the reference's GPU code on the same machine")
+    ap.add_argument("--details", default="", help="also write the full record (notes, per-launch distributions) to this file")
     ap.add_argument("--rows", type=int, default=0, help="override the headline workload's row count (profiling)")
     ap.add_argument("--profile", action="store_true", help="run only warm-up and timed steps (for ncu captures)")
     args = ap.parse_args()

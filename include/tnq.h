@@ -42,14 +42,14 @@ typedef enum { TNQ_SCALE_IS_SCALE = 0, TNQ_SCALE_IS_AMAX = 1 } tnq_scale_source;
  * leave it ready for the next call.  Two calls that share a workspace must be
  * ordered (same stream); use one workspace per concurrent stream.
  * Layout (uint32 words): [0] ticket  [1] amax as fp32 bits  [2] scale (fp32)
- * [3] device status  [4..7] grid-barrier words of the single-launch cast
+ * [3] device status  [5..9] call counter and grid-exchange words of the single-launch cast
  * [16..] per-CTA partial maxima.
  * Device status: every wait inside a kernel is bounded (about one second); a wait
  * that gives up stores TNQ_ETIMEOUT in word [3] (or in the `status` word an entry
  * point takes) and the kernel returns with its outputs incomplete.  Nothing reads
  * the word for the caller: read it after synchronising the stream.  A kernel that
- * left early may not have rewound words [0] and [4..7], so after a TNQ_ETIMEOUT
- * zero the first 64 bytes of the workspace before using it again. */
+ * left early may not have rewound words [0] and [6..9], so after a TNQ_ETIMEOUT zero the
+ * first 64 bytes of the workspace before using it again. */
 #define TNQ_WORKSPACE_BYTES 16384
 #define TNQ_WS_AMAX_WORD 1
 #define TNQ_WS_SCALE_WORD 2
@@ -76,6 +76,10 @@ int tnq_abi_version(void);
  * bit 1 = it stores with evict_first. */
 #define TNQ_OPT_L2_KEEP_MB 3
 #define TNQ_OPT_CAST_L2_MODE 4
+/* TNQ_OPT_CAST_PAIR (default 1): a per-tensor cast of bf16 input that walks the tensor forwards
+ * (delayed scale, plain cast) takes 64 contiguous input bytes per thread and step and writes their
+ * 32 fp8 bytes with one 256-bit store. */
+#define TNQ_OPT_CAST_PAIR 5
 int tnq_set_option(int option, int value);
 
 /* amax = max|x| over n elements, written as fp32 to ws word TNQ_WS_AMAX_WORD and,
@@ -123,6 +127,11 @@ int tnq_delayed_scale_update(float* amax_history, float* amax, float* scale, int
 int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
                            const float* scale, int scale_kind, int saturated, float* abs_max_inout,
                            void* out, void* out_t, uint32_t* status, tnq_stream_t stream);
+/* Tuning switch for the transposing cast, same results either way.  variant + 4 * policy:
+ * variant 0 = both outputs stored straight to global memory, 1 (default) = the transposed output is
+ * staged in shared memory and written by TMA stores when rows % 16 == 0; policy bits as for
+ * tnq_mxfp8_set_store_variant. */
+int tnq_cast_transpose_set_store_variant(int variant);
 
 /* RMSNorm fused into the row-wise dynamic e4m3 cast, bf16 [rows, cols] in, one read:
  *   y = bf16((f32(x) * rstd) * f32(weight)),  rstd = 1 / sqrt(mean(f32(x)^2) + eps)   per row
@@ -199,6 +208,16 @@ int tnq_nvfp4_gemm(const void* a_packed, const void* b_packed, const void* sf_a,
 int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
                          void* workspace, float* scale_out, tnq_stream_t stream);
 
+/* Diagnostic twin of tnq_fp8_dynamic_cast (bf16 -> e4m3, single-launch path only, else
+ * TNQ_EUNSUPPORTED): the same kernel built with time stamps, for splitting its duration into
+ * phases.  stamps: device buffer of 8 uint64 per CTA (256 CTAs at most); words 0..3 are SM
+ * clock readings at kernel entry / slab loaded and CTA maximum known / grid-wide exchange
+ * done / last store issued, words 4..7 the global nanosecond timer at the same four points.
+ * *grid_out (host, nullable) receives the number of CTAs.
+ * No counterpart in the reference. */
+int tnq_fp8_dynamic_cast_profile(const void* x, void* out, int64_t n, void* workspace, float* scale_out,
+                                 unsigned long long* stamps, int* grid_out, tnq_stream_t stream);
+
 /* The same cast as tnq_fp8_dynamic_cast for callers that cannot provide (or create)
  * device scratch: plug-ins that receive only tensors and a stream from their host
  * framework, processes whose device memory is entirely owned by a pool reserved at
@@ -251,6 +270,11 @@ int tnq_rowwise_set_group(int threads_per_row);
 int tnq_mxfp8_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype, void* q_row,
                        void* sf_row, void* q_col, void* sf_col, int e8m0_mode, int scale_layout,
                        uint32_t* status, tnq_stream_t stream);
+/* Tuning switch for the row + column quantizer, same results either way.  variant + 4 * policy:
+ * variant 0 = both passes store straight to global memory, 1 (default) = the transposed payload is
+ * staged in shared memory and written by TMA stores; policy bit 0 (default on) = input tiles are
+ * loaded with an L2 evict-first policy, bit 1 = so are the stored lines. */
+int tnq_mxfp8_set_store_variant(int variant);
 
 /* NVFP4: 16-element blocks along cols, e4m3 block scales, two e2m1 codes per byte
  * (low nibble first), fp32 global scale.  *global_amax is max|x| of the whole

@@ -168,6 +168,21 @@ def test_swiglu_mxfp8(shape, mode):
     assert torch.equal(as_u8(q2), as_u8(q)) and torch.equal(sf2.cpu(), oracle.to_blocked(want_sf))
 
 
+def test_swiglu_large_negative_gate():
+    """Gate values in (-88.7, -87.3): 1 + exp(-a) lies in (2^126, 2^128), where an approximate division
+    would return 0 although silu(a) is about -5e-37, still a normal bf16 value.  The activation must stay
+    within one bf16 step of the eager result there too, and beyond -88.8 (exp overflows) it is -0."""
+    vals = torch.tensor([-86.0, -87.0, -87.5, -88.0, -88.5, -88.7, -89.0, -100.0, -3.0, 0.0, 2.0, 88.0])
+    a = vals.repeat(64 * 32 // vals.numel() + 1)[: 64 * 32].reshape(64, 32).to(torch.bfloat16)
+    b = torch.full_like(a, 1.5)
+    q, scale, y = swiglu_rowwise_quant(a.to(DEV), b.to(DEV), return_activation=True)
+    want = oracle.swiglu(a, b)
+    d = _ulp_distance(y.cpu(), want)
+    assert d.max().item() <= 1
+    nz = want.float() != 0
+    assert bool(((y.cpu().float() != 0) == nz).all())  # nothing that should be non-zero was flushed to zero
+
+
 def test_swiglu_argument_checks():
     a = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(ValueError):

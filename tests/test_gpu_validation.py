@@ -114,7 +114,8 @@ def test_check_status_reports_and_repairs_the_workspace():
     _lib.check_status(x.device)  # clean
     ws = _lib.workspace(x.device)
     ws[_lib.WS_STATUS_WORD] = 6
-    ws[4] = 3  # bar_count as an abandoned grid barrier would leave it
+    ws[6] = 3  # arrival counters of the grid-wide exchange as an abandoned call would leave them
+    ws[8] = 3
     with pytest.raises(_lib.TnqError) as e:
         _lib.check_status(x.device, what="tnq_fp8_dynamic_cast")
     assert e.value.status == 6

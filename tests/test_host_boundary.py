@@ -52,7 +52,7 @@ def test_check_status_raises_and_rezeroes(monkeypatch):
     monkeypatch.setattr(_lib, "_workspaces", fake)
     _lib.check_status(0)  # clean: nothing raised
     ws[_lib.WS_STATUS_WORD] = 6
-    ws[4] = 17  # a grid-barrier counter the kernel did not rewind
+    ws[6] = 17  # an arrival counter the kernel did not rewind
     ws[100] = 5  # beyond the header: untouched
     with pytest.raises(_lib.TnqError) as e:
         _lib.check_status(0, what="tnq_mxfp8_quantize")

@@ -37,12 +37,14 @@ SIGNATURES = {
     "tnq_fp8_amax": [_p, _i64, _i, _i, _p, _p, _p],
     "tnq_fp8_scaled_cast": [_p, _p, _i64, _i, _i, _p, _i, _i, _p, _p, _p],
     "tnq_fp8_dynamic_cast": [_p, _p, _i64, _i, _i, _p, _p, _p],
+    "tnq_fp8_dynamic_cast_profile": [_p, _p, _i64, _p, _p, _p, _p, _p],
     "tnq_fp8_dynamic_cast_static": [_p, _p, _i64, _i, _i, _p, _p],
     "tnq_fp8_dynamic_cast_static_max_elements": [],
     "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p],
     "tnq_rowwise_set_tma": [_i],
     "tnq_rowwise_set_group": [_i],
     "tnq_mxfp8_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _p],
+    "tnq_mxfp8_set_store_variant": [_i],
     "tnq_nvfp4_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p, _p],
     "tnq_pack_fp4_codes": [_p, _i64, _i64, _p, _p],
     "tnq_to_blocked": [_p, _i64, _i64, _p, _p],
@@ -54,6 +56,7 @@ SIGNATURES = {
     "tnq_fp8_sharded_cast": [_p, _p, _i64, _i, _i, _p, _p, _i, _i, ctypes.c_uint32, _p, _p],
     "tnq_sharded_amax": [_p, _i64, _i, _p, _p, _i, _i, ctypes.c_uint32, _p, _p],
     "tnq_fp8_cast_transpose": [_p, _i64, _i64, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p],
+    "tnq_cast_transpose_set_store_variant": [_i],
     "tnq_rmsnorm_fp8_rowwise": [_p, _p, ctypes.c_float, _i64, _i64, _p, _p, _p, _p],
     "tnq_rmsnorm_mxfp8": [_p, _p, ctypes.c_float, _i64, _i64, _p, _p, _i, _i, _p, _p],
     "tnq_swiglu_fp8_rowwise": [_p, _p, _i64, _i64, _p, _p, _p, _p],
@@ -158,7 +161,7 @@ def require_cuda(t: torch.Tensor, what: str):
 
 
 #: entry points that launch nothing (no status to look at afterwards)
-_NO_LAUNCH = {"tnq_set_option", "tnq_rowwise_set_tma", "tnq_rowwise_set_group", "tnq_exchange_create",
+_NO_LAUNCH = {"tnq_set_option", "tnq_mxfp8_set_store_variant", "tnq_cast_transpose_set_store_variant", "tnq_rowwise_set_tma", "tnq_rowwise_set_group", "tnq_exchange_create",
               "tnq_exchange_open", "tnq_exchange_close", "tnq_exchange_destroy", "tnq_exchange_status"}
 
 #: most recently used (device, stream) -> workspace; bounded so that a program that keeps creating

@@ -143,6 +143,20 @@ __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w &
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t m, uint32_t w) {
   return __vmaxu2(m, w & 0x7fff7fffu);
 }
+// The same in ONE instruction per word: max of the magnitudes of two bf16 pairs; the sign bits of the
+// result are meaningless (mask them off at the end) and any NaN makes the half the canonical NaN
+// 0x7fff, which is above infinity in the integer order used to fold the result.
+__device__ __forceinline__ uint32_t absmax_bf16x2_1op(uint32_t m, uint32_t w) {
+  uint32_t r;
+  asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(w));
+  return r;
+}
+// ... and for one fp32 (bit pattern in and out)
+__device__ __forceinline__ uint32_t absmax_f32_1op(uint32_t m, uint32_t w) {
+  float r;
+  asm("max.NaN.xorsign.abs.f32 %0, %1, %2;" : "=f"(r) : "f"(__uint_as_float(m)), "f"(__uint_as_float(w)));
+  return __float_as_uint(r);
+}
 __device__ __forceinline__ uint32_t fold_u16x2(uint32_t m) { return max(m & 0xffffu, m >> 16); }
 __device__ __forceinline__ float bf16bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
 
@@ -370,6 +384,33 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, in
       "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+// 2-D tiled TMA store this CTA's shared memory -> global, tracked by the issuing thread's bulk
+// async-group.  The part of the box that lies outside the tensor is not written.  x * element
+// size must be a multiple of 16 bytes and neither coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+               "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+// the same two copies carrying an L2 eviction-priority policy (createpolicy)
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const void* tmap, int32_t x, int32_t y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], "
+      "[%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const void* tmap, uint32_t smem_src, int32_t x, int32_t y, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(tmap),
+               "r"(smem_src), "r"(x), "r"(y), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_group_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's committed bulk groups have finished READING shared memory (it may be reused)
+__device__ __forceinline__ void bulk_group_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have completed altogether
+__device__ __forceinline__ void bulk_group_wait() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

@@ -75,8 +75,15 @@ __device__ __forceinline__ uint32_t swiglu_pk(uint32_t a_pk, uint32_t b_pk) {
   float a0, a1, b0, b1;
   widen_pk(a_pk, a0, a1);
   widen_pk(b_pk, b0, b1);
-  // ex2.approx and the approximate division: relative error near 2^-21, far below half a bf16 step
-  const float s0 = __fdividef(a0, __fadd_rn(1.0f, __expf(-a0))), s1 = __fdividef(a1, __fadd_rn(1.0f, __expf(-a1)));
+  // ex2.approx and the approximate division: relative error near 2^-21, far below half a bf16 step.
+  // The approximate division returns 0 for a divisor in (2^126, 2^128), which 1 + exp(-a) reaches for a
+  // in about (-88.7, -87.3) although the quotient there (about -5e-37) is still a normal bf16 value.
+  // Both operands are therefore scaled by 2^-4 first (exact), which keeps the divisor below 2^124.
+  auto silu = [](float a) {
+    const float den = __fadd_rn(1.0f, __expf(-a));
+    return __fdividef(__fmul_rn(a, 0.0625f), __fmul_rn(den, 0.0625f));
+  };
+  const float s0 = silu(a0), s1 = silu(a1);
   uint32_t s_pk;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(s_pk) : "f"(s1), "f"(s0));
   float t0, t1;

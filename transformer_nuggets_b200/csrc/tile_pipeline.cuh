@@ -110,6 +110,30 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
   Op::finish(p, state);
 }
 
+// ---- outputs staged in shared memory and written by TMA stores (row + column kernels)
+constexpr int kStagesTs = 2;
+constexpr int kStageOutBytes = kTileCols * 128;  // transposed fp8 tile: 128 columns x 128 bytes
+// 1 KiB alignment slack (the 128-byte swizzle of the staging tile), the staging tile, input stages,
+// barriers + counters, four scale atoms
+constexpr int kTsSmemBytes = 1024 + kStageOutBytes + kStagesTs * kTileBytes + 64 + 4 * 512;
+
+// The 2 x 32 payload bytes of a column-pass thread into the transposed staging tile
+// [128 columns][128 bytes] that a TMA store with the 128-byte swizzle reads: the 16-byte chunk j
+// of staging row c lives at chunk j ^ (c & 7).  Two-way bank conflicts at most.
+__device__ __forceinline__ void stage_transposed(uint32_t stg, int t, const uint32_t (&lo)[8], const uint32_t (&hi)[8]) {
+  const int w = t & 63, rb = t >> 6;
+  const uint32_t c0 = 2 * w, c1 = 2 * w + 1;
+  const uint32_t r0 = stg + c0 * 128, r1 = stg + c1 * 128;
+  const uint32_t j0 = 2 * rb, j1 = 2 * rb + 1;
+  auto sts128 = [](uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+  };
+  sts128(r0 + ((j0 ^ (c0 & 7)) << 4), lo[0], lo[1], lo[2], lo[3]);
+  sts128(r0 + ((j1 ^ (c0 & 7)) << 4), lo[4], lo[5], lo[6], lo[7]);
+  sts128(r1 + ((j0 ^ (c1 & 7)) << 4), hi[0], hi[1], hi[2], hi[3]);
+  sts128(r1 + ((j1 ^ (c1 & 7)) << 4), hi[4], hi[5], hi[6], hi[7]);
+}
+
 }  // namespace tnq
 
 // ------------------------------------------------------------------ host: tensor map
@@ -148,6 +172,43 @@ inline int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64
     return TNQ_ECUDA;
   }
   return TNQ_OK;
+}
+
+// Tensor map of a row-major [outer, inner] matrix of bytes for TMA stores of 128 x 128-byte
+// boxes out of shared memory.  `swizzle128`: the shared-memory tile uses the 128-byte swizzle
+// (16-byte chunk j of row r at chunk j ^ (r & 7); tile base 1 KiB aligned).  Requires a
+// 16-byte aligned base and inner % 16 == 0.
+inline int make_byte_store_map(CUtensorMap* map, void* base, int64_t outer, int64_t inner, bool swizzle128) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return TNQ_ECUDA;
+  const cuuint64_t gdim[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  const cuuint64_t gstride[1] = {(cuuint64_t)inner};
+  const cuuint32_t box[2] = {128u, 128u};
+  const cuuint32_t estride[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = (int)r;
+    return TNQ_ECUDA;
+  }
+  return TNQ_OK;
+}
+
+// resident CTAs of a kernel with `smem` bytes of dynamic shared memory (cached per device)
+template <auto Kernel, int Threads, int Smem>
+inline int resident_ctas_smem() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem) != cudaSuccess) return -1;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, Kernel, Threads, Smem) != cudaSuccess || per_sm < 1)
+      return -1;
+    cached[dev] = per_sm * sm_count();
+  }
+  return cached[dev];
 }
 
 template <auto Kernel, int Threads>
