@@ -127,10 +127,10 @@ int tnq_delayed_scale_update(float* amax_history, float* amax, float* scale, int
 int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
                            const float* scale, int scale_kind, int saturated, float* abs_max_inout,
                            void* out, void* out_t, uint32_t* status, tnq_stream_t stream);
-/* Tuning switch for the transposing cast, same results either way.  variant + 4 * policy:
- * variant 0 = both outputs stored straight to global memory, 1 (default) = the transposed output is
- * staged in shared memory and written by TMA stores when rows % 16 == 0; policy bits as for
- * tnq_mxfp8_set_store_variant. */
+/* Tuning switch for the transposing cast, same results either way.  1 (default): every element is
+ * converted once, the fp8 bytes are transposed in shared memory and out_t is written by TMA stores
+ * (rows % 16 == 0, else variant 0 runs); 0: both outputs converted separately and stored straight to
+ * global memory. */
 int tnq_cast_transpose_set_store_variant(int variant);
 
 /* RMSNorm fused into the row-wise dynamic e4m3 cast, bf16 [rows, cols] in, one read:

@@ -9,10 +9,10 @@
 // outputs hold identical bytes.  Optional side output: abs_max = max(abs_max, max|x|) for
 // delayed scaling.
 //
-// 128 x 128 bf16 tiles arrive by 2-D TMA into a three-stage mbarrier ring.  Threads 0-255
-// make the row-major output, threads 256-511 the transposed output.  Each element is converted twice rather than staged through a second
-// shared-memory tile: the conversions are cheap and the kernel is bound by its three
-// global streams.
+// 128 x 128 bf16 tiles arrive by 2-D TMA into an mbarrier ring.  Two kernels: k_cast_transpose_bt
+// (default) converts every element once and transposes the fp8 bytes in shared memory;
+// k_cast_transpose (threads 0-255 make the row-major output, threads 256-511 the transposed one, every
+// element converted twice, plain global stores) serves the shapes the first cannot take.
 #include <atomic>
 
 #include "tile_pipeline.cuh"
@@ -173,116 +173,6 @@ __global__ void __launch_bounds__(512, 2)
   }
 }
 
-// The same cast with the transposed output staged in shared memory and written by TMA stores:
-// out_t rows receive whole 128-byte lines from the copy engine instead of 32-byte pieces from four
-// warps (112.9 -> 108.1 us at 16384 x 8192; with the input tiles loaded under an L2 evict-first
-// policy, `tuning` bit 0: 104.0 us).  Three input stages and the 16 KiB staging tile just fit twice
-// on an SM because the dynamic shared memory is declared 1 KiB aligned (the 128-byte swizzle of the
-// staging tile needs that) instead of being aligned by hand with 1 KiB of slack; the kernel checks
-// the alignment and refuses to run otherwise.  Needs a 16-byte row pitch of out_t (rows % 16 == 0).
-constexpr int kCtStages = 3;
-constexpr int kCtSmemBytes = kStageOutBytes + kCtStages * kTileBytes + 64;
-
-template <int OUT, bool SAT>
-__global__ void __launch_bounds__(512, 2)
-    k_cast_transpose_ts(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap map_col, CastTParams p,
-                        uint32_t tiles_r, uint32_t tiles_c, uint32_t* status, int tuning) {
-  extern __shared__ __align__(1024) uint8_t tnq_dyn_smem_1k[];
-  uint8_t* const base = tnq_dyn_smem_1k;
-  const uint32_t stg_col = smem_u32(base);
-  if ((stg_col & 1023u) != 0u) {  // never seen; a misplaced staging tile would scramble out_t silently
-    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_EALIGN);
-    return;
-  }
-  uint8_t* const tiles = base + kStageOutBytes;
-  const uint32_t tile0 = smem_u32(tiles);
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(tiles + kCtStages * kTileBytes);
-  uint32_t* const done = reinterpret_cast<uint32_t*>(tiles + kCtStages * kTileBytes + 32);
-  uint32_t* const cta_max = done + kCtStages;
-  const uint32_t ntiles = tiles_r * tiles_c;
-  const uint32_t first = blockIdx.x;
-  const uint32_t count = first < ntiles ? (ntiles - first + gridDim.x - 1) / gridDim.x : 0;
-  const int group = threadIdx.x >> 8, gtid = threadIdx.x & 255;
-  const bool hint_ld = (tuning & 1) != 0, hint_st = (tuning & 2) != 0;
-  const uint64_t pol = l2_policy_evict_first();
-
-  TileCursor cur, ahead;
-  cur.init(first, gridDim.x, tiles_c);
-  ahead = cur;
-  auto issue = [&](uint32_t s) {
-    mbar_expect_tx(&bars[s], kTileBytes);
-    const int32_t x = (int32_t)(ahead.tc * kTileCols), y = (int32_t)(ahead.tr * kTileRows);
-    if (hint_ld) tma_load_2d_hint(tiles + s * kTileBytes, &tmap, x, y, &bars[s], pol);
-    else tma_load_2d(tiles + s * kTileBytes, &tmap, x, y, &bars[s]);
-  };
-  if (threadIdx.x == 0) {
-    prefetch_tmap(&tmap);
-    prefetch_tmap(&map_col);
-    for (int s = 0; s < kCtStages; ++s) {
-      mbar_init(&bars[s], 1);
-      done[s] = 0;
-    }
-    *cta_max = 0;
-    fence_mbar_init();
-  }
-  __syncthreads();
-  for (uint32_t s = 0; s < (uint32_t)kCtStages; ++s) {
-    if (threadIdx.x == 0 && s < count) issue(s);
-    ahead.advance();
-  }
-  const float v = *p.scale;
-  const float scale = p.scale_kind == TNQ_SCALE_IS_AMAX ? scale_from_amax(v, Fp8Traits<OUT>::kMax) : v;
-  uint32_t m = 0;
-
-  uint32_t s = 0, phase = 0;
-  for (uint32_t k = 0; k < count; ++k) {
-    if (!mbar_wait(&bars[s], phase)) {
-      if (gtid == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_ETIMEOUT);
-      break;
-    }
-    const uint32_t tile = tile0 + s * kTileBytes;
-    const bool full = (int64_t)(cur.tr + 1) * kTileRows <= p.rows && (int64_t)(cur.tc + 1) * kTileCols <= p.cols;
-    auto release_stage = [&]() {  // gtid == 0, after the group's barrier: the group no longer reads the tile
-      __threadfence_block();
-      if (atomicAdd(&done[s], 1u) == 1u) {
-        atomicExch(&done[s], 0u);
-        if (k + kCtStages < count) issue(s);
-      }
-    };
-    if (group == 0) {
-      if (full) ct_row_pass<OUT, SAT, true>(p, scale, m, tile, cur.tr, cur.tc, gtid);
-      else ct_row_pass<OUT, SAT, false>(p, scale, m, tile, cur.tr, cur.tc, gtid);
-      named_barrier<1, 256>();
-      if (gtid == 0) release_stage();
-    } else {
-      uint32_t lo[8], hi[8];
-      ct_col_compute<OUT, SAT>(scale, tile, gtid, lo, hi);
-      if (gtid == 0) bulk_group_wait_read();  // the previous tile's store has read the staging tile
-      named_barrier<2, 256>();
-      if (gtid == 0) release_stage();
-      stage_transposed(stg_col, gtid, lo, hi);
-      fence_proxy_async();
-      named_barrier<3, 256>();
-      if (gtid == 0) {  // the part of the box outside the matrix is clipped by the copy engine
-        const int32_t x = (int32_t)(cur.tr * kTileRows), y = (int32_t)(cur.tc * kTileCols);
-        if (hint_st) tma_store_2d_hint(&map_col, stg_col, x, y, pol);
-        else tma_store_2d(&map_col, stg_col, x, y);
-        bulk_group_commit();
-      }
-    }
-    cur.advance();
-    ahead.advance();
-    if (++s == (uint32_t)kCtStages) s = 0, phase ^= 1u;
-  }
-  if (gtid == 0) bulk_group_wait();  // shared memory must outlive the stores that read it
-  if (p.abs_max != nullptr && group == 0) {
-    const uint32_t wm = warp_max_u32(fold_u16x2(m));
-    if ((gtid & 31) == 0 && wm != 0u) atomicMax(cta_max, wm);
-    named_barrier<1, 256>();
-    if (gtid == 0) atomicMax(reinterpret_cast<int*>(p.abs_max), (int)(*cta_max << 16));
-  }
-}
-
 }  // namespace tnq
 
 using namespace tnq;
@@ -299,21 +189,148 @@ static int launch_cast_transpose(const CUtensorMap& map, const CastTParams& p, u
   return check_launch();
 }
 
-// variant: 0 = direct global stores, 1 (default) = transposed output through shared memory + TMA
-// stores where its row pitch allows; tuning: L2 policy bits of the TMA-store kernel
+namespace tnq {
+
+// The same result with every element converted ONCE: all 512 threads convert the tile row-major
+// (8 fp8 bytes per thread and row: stored to `out` and, XOR-swizzled, into a 128 x 128-byte fp8 tile in
+// shared memory), then all 512 threads transpose that tile in 4 x 4-byte squares - four conflict-free
+// 4-byte shared loads, eight byte permutes, four conflict-free 4-byte stores into the staging tile that
+// one TMA store (128-byte swizzle) sends to out_t, so that every out_t row receives a full 128-byte
+// line.  Input tiles are loaded with an L2 evict-first policy.  16384 x 8192: 101.7 us against 112.9 -
+// 115.6 us for the kernel above (converting twice with a staged TMA store for out_t: 104.0 - 105.3 us).
+// Needs a 16-byte row pitch of out_t (rows % 16 == 0).  The dynamic shared memory is declared 1 KiB
+// aligned (the swizzle needs that); the kernel checks it and refuses to run otherwise.
+// Shared memory: [transposed staging 16 KiB][fp8 tile 16 KiB][2 input stages][barriers].
+constexpr int kBtStages = 2;
+constexpr int kBtSmemBytes = 2 * kStageOutBytes + kBtStages * kTileBytes + 64;
+
+template <int OUT, bool SAT>
+__global__ void __launch_bounds__(512, 2)
+    k_cast_transpose_bt(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap map_col, CastTParams p,
+                        uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
+  extern __shared__ __align__(1024) uint8_t tnq_dyn_smem_1k[];
+  uint8_t* const base = tnq_dyn_smem_1k;
+  const uint32_t stg_t = smem_u32(base);  // transposed staging, read by the TMA store
+  if ((stg_t & 1023u) != 0u) {            // never seen; a misplaced staging tile would scramble out_t silently
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_EALIGN);
+    return;
+  }
+  const uint32_t stg_q = stg_t + kStageOutBytes;  // row-major fp8 tile, word w of row r at word w ^ (r >> 2)
+  uint8_t* const tiles = base + 2 * kStageOutBytes;
+  const uint32_t tile0 = smem_u32(tiles);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(tiles + kBtStages * kTileBytes);
+  uint32_t* const cta_max = reinterpret_cast<uint32_t*>(tiles + kBtStages * kTileBytes + 32);
+  const uint32_t ntiles = tiles_r * tiles_c;
+  const uint32_t first = blockIdx.x;
+  const uint32_t count = first < ntiles ? (ntiles - first + gridDim.x - 1) / gridDim.x : 0;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const uint64_t pol = l2_policy_evict_first();
+
+  TileCursor cur, ahead;
+  cur.init(first, gridDim.x, tiles_c);
+  ahead = cur;
+  auto issue = [&](uint32_t s) {
+    mbar_expect_tx(&bars[s], kTileBytes);
+    tma_load_2d_hint(tiles + s * kTileBytes, &tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s], pol);
+  };
+  if (t == 0) {
+    prefetch_tmap(&tmap);
+    prefetch_tmap(&map_col);
+    for (int s = 0; s < kBtStages; ++s) mbar_init(&bars[s], 1);
+    *cta_max = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  for (uint32_t s = 0; s < (uint32_t)kBtStages; ++s) {
+    if (t == 0 && s < count) issue(s);
+    ahead.advance();
+  }
+  const float v = *p.scale;
+  const float scale = p.scale_kind == TNQ_SCALE_IS_AMAX ? scale_from_amax(v, Fp8Traits<OUT>::kMax) : v;
+  uint32_t m = 0;
+
+  // conversion: thread = 16-byte piece `piece` of rows r_in, r_in + 32, r_in + 64, r_in + 96
+  const int piece = t & 15, r_in = t >> 4;
+  // transposition: lane = group of four rows, warp = two groups of four columns
+  const int rg = lane;
+
+  uint32_t s = 0, phase = 0;
+  for (uint32_t k = 0; k < count; ++k) {
+    if (!mbar_wait(&bars[s], phase)) {
+      if (t == 0 && status != nullptr) atomicExch(status, (uint32_t)TNQ_ETIMEOUT);
+      break;
+    }
+    const uint32_t tile = tile0 + s * kTileBytes;
+    const bool full = (int64_t)(cur.tr + 1) * kTileRows <= p.rows && (int64_t)(cur.tc + 1) * kTileCols <= p.cols;
+    const int64_t c = (int64_t)cur.tc * kTileCols + piece * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = i * 32 + r_in;
+      const int64_t r = (int64_t)cur.tr * kTileRows + row;
+      const uint4 q = lds128(tile + row * 256 + piece * 16);  // zeros outside the matrix
+      m = absmax_bf16x2_1op(absmax_bf16x2_1op(absmax_bf16x2_1op(absmax_bf16x2_1op(m, q.x), q.y), q.z), q.w);
+      const uint2 o = quant8_bf16<OUT, SAT>(q, scale);
+      if (full || (r < p.rows && c < p.cols)) stg64(p.out + r * p.cols + c, o);
+      // words 2 piece, 2 piece + 1 of the row go to word positions (2 piece) ^ g and (2 piece + 1) ^ g, g = row >> 2:
+      // the same aligned pair with g's low bit cleared, the two words swapped when g is odd
+      const uint32_t g = (uint32_t)row >> 2;
+      const uint32_t dst = stg_q + row * 128 + 4 * ((2 * piece) ^ (g & ~1u));
+      const bool swap = (g & 1u) != 0;
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dst), "r"(swap ? o.y : o.x), "r"(swap ? o.x : o.y) : "memory");
+    }
+    if (t == 0) bulk_group_wait_read();  // the previous tile's store has read the transposed staging tile
+    __syncthreads();                     // tile converted: its stage is free, the fp8 tile is complete
+    if (t == 0 && k + kBtStages < count) issue(s);  // `ahead` is the tile kBtStages after `cur`
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t cg = 2 * warp + h;  // columns 4 cg .. 4 cg + 3
+      const uint32_t src = stg_q + (4 * rg) * 128 + 4 * (cg ^ (uint32_t)rg);
+      const uint32_t a = lds32(src), b = lds32(src + 128), c4 = lds32(src + 256), d = lds32(src + 384);
+      const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c4, d, 0x5140);
+      const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c4, d, 0x7362);
+      const uint32_t o[4] = {__byte_perm(t0, t1, 0x5410), __byte_perm(t0, t1, 0x7632), __byte_perm(t2, t3, 0x5410),
+                             __byte_perm(t2, t3, 0x7632)};
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {  // column 4 cg + kk, rows 4 rg .. 4 rg + 3: chunk rg >> 2, swizzled by the column
+        const uint32_t col = 4 * cg + kk;
+        const uint32_t dst = stg_t + col * 128 + ((((uint32_t)rg >> 2) ^ (col & 7u)) << 4) + 4 * ((uint32_t)rg & 3u);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(o[kk]) : "memory");
+      }
+    }
+    fence_proxy_async();
+    __syncthreads();  // transposed tile complete (and the fp8 tile may be overwritten by the next conversion)
+    if (t == 0) {     // the part of the box outside the matrix is clipped by the copy engine
+      tma_store_2d(&map_col, stg_t, (int32_t)(cur.tr * kTileRows), (int32_t)(cur.tc * kTileCols));
+      bulk_group_commit();
+    }
+    cur.advance();
+    ahead.advance();
+    if (++s == (uint32_t)kBtStages) s = 0, phase ^= 1u;
+  }
+  if (t == 0) bulk_group_wait();  // shared memory must outlive the stores that read it
+  if (p.abs_max != nullptr) {
+    const uint32_t wm = warp_max_u32(fold_u16x2(m & 0x7fff7fffu));
+    if (lane == 0 && wm != 0u) atomicMax(cta_max, wm);
+    __syncthreads();
+    if (t == 0) atomicMax(reinterpret_cast<int*>(p.abs_max), (int)(*cta_max << 16));
+  }
+}
+
+}  // namespace tnq
+
+// variant: 0 = both outputs converted separately and stored straight to global memory (the only path for
+// shapes whose out_t row pitch is not a multiple of 16 bytes), 1 (default) = convert once, transpose the
+// fp8 bytes in shared memory, TMA store
 static std::atomic<int> g_ct_store_variant{1};
-static std::atomic<int> g_ct_tuning{1};
 extern "C" int tnq_cast_transpose_set_store_variant(int v) {
-  const int variant = v & 3, tuning = v >> 2;
-  if (v < 0 || variant > 1 || tuning > 3) return TNQ_EINVAL;
-  g_ct_store_variant.store(variant, std::memory_order_relaxed);
-  g_ct_tuning.store(tuning, std::memory_order_relaxed);
+  if (v < 0 || v > 1) return TNQ_EINVAL;
+  g_ct_store_variant.store(v, std::memory_order_relaxed);
   return TNQ_OK;
 }
 
 template <int OUT, bool SAT>
-static int launch_cast_transpose_ts(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
-  const int cap = resident_ctas_smem<k_cast_transpose_ts<OUT, SAT>, 512, kCtSmemBytes>();
+static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
+  const int cap = resident_ctas_smem<k_cast_transpose_bt<OUT, SAT>, 512, kBtSmemBytes>();
   if (cap < 1) return cuda_fail(cudaGetLastError());
   CUtensorMap map_col;
   int rc = make_byte_store_map(&map_col, p.out_t, p.cols, p.rows, true);
@@ -321,15 +338,14 @@ static int launch_cast_transpose_ts(const CUtensorMap& map, const CastTParams& p
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_cast_transpose_ts<OUT, SAT><<<grid, 512, kCtSmemBytes, stream>>>(map, map_col, p, (uint32_t)tiles_r, (uint32_t)tiles_c,
-                                                                      status, g_ct_tuning.load(std::memory_order_relaxed));
+  k_cast_transpose_bt<OUT, SAT><<<grid, 512, kBtSmemBytes, stream>>>(map, map_col, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
   return check_launch();
 }
 
 template <int OUT, bool SAT>
 static int launch_cast_transpose_any(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
   if (g_ct_store_variant.load(std::memory_order_relaxed) == 1 && p.rows % 16 == 0 && aligned16(p.out_t))
-    return launch_cast_transpose_ts<OUT, SAT>(map, p, status, stream);
+    return launch_cast_transpose_bt<OUT, SAT>(map, p, status, stream);
   return launch_cast_transpose<OUT, SAT>(map, p, status, stream);
 }
 

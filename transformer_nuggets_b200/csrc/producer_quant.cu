@@ -78,10 +78,11 @@ __device__ __forceinline__ uint32_t swiglu_pk(uint32_t a_pk, uint32_t b_pk) {
   // ex2.approx and the approximate division: relative error near 2^-21, far below half a bf16 step.
   // The approximate division returns 0 for a divisor in (2^126, 2^128), which 1 + exp(-a) reaches for a
   // in about (-88.7, -87.3) although the quotient there (about -5e-37) is still a normal bf16 value.
-  // Both operands are therefore scaled by 2^-4 first (exact), which keeps the divisor below 2^124.
+  // Both operands are therefore scaled by 2^-4 (exact), which keeps the divisor below 2^124.
+  // (1 + e) / 16 comes out of one FMA bit-identical to the sum rounded and then scaled.
   auto silu = [](float a) {
-    const float den = __fadd_rn(1.0f, __expf(-a));
-    return __fdividef(__fmul_rn(a, 0.0625f), __fmul_rn(den, 0.0625f));
+    const float den16 = fmaf(__expf(-a), 0.0625f, 0.0625f);
+    return __fdividef(__fmul_rn(a, 0.0625f), den16);
   };
   const float s0 = silu(a0), s1 = silu(a1);
   uint32_t s_pk;
