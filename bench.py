@@ -889,6 +889,21 @@ def _bench_delayed(dev, res, timed, peak, ws, stream):
                      "algorithmic_bytes_per_element": bpe, "note": f"{rows}x{cols}, delayed scale, saturated, abs_max side output"}
     del xb, q
 
+    # the state update between two steps (amax history -> next scale) for a model's worth of tensors in one launch
+    tensors, hist = 1024, 16
+    history = torch.rand(tensors, hist, dtype=torch.float32, device=dev)
+    amaxes = torch.rand(tensors, dtype=torch.float32, device=dev)
+    scales = torch.ones(tensors, dtype=torch.float32, device=dev)
+
+    def upd(_):
+        _lib.call("tnq_delayed_scale_update", history.data_ptr(), amaxes.data_ptr(), scales.data_ptr(), tensors, hist,
+                  _lib.FP8_E4M3, stream)
+
+    ms = timed(upd, [None])
+    nbytes = 4.0 * tensors * (2 * hist + 2)  # history read and written back, amax read and cleared, scale written
+    res["delayed_scale_update"] = {"us": ms * 1e3, "GBps": nbytes / (ms * 1e-3) / 1e9, "tensors": tensors, "history_len": hist,
+                                   "note": "one launch for all tensors; launch-latency bound (146 KB moved)"}
+
 
 def _bench_rmsnorm(dev, res, timed, peak, stream):
     """RMSNorm fused into the row-wise e4m3 cast (bf16 16384 x 8192): 2 B read + 1 B written per

@@ -75,14 +75,19 @@ __device__ __forceinline__ uint32_t swiglu_pk(uint32_t a_pk, uint32_t b_pk) {
   float a0, a1, b0, b1;
   widen_pk(a_pk, a0, a1);
   widen_pk(b_pk, b0, b1);
-  // ex2.approx and the approximate division: relative error near 2^-21, far below half a bf16 step.
-  // The approximate division returns 0 for a divisor in (2^126, 2^128), which 1 + exp(-a) reaches for a
-  // in about (-88.7, -87.3) although the quotient there (about -5e-37) is still a normal bf16 value.
-  // Both operands are therefore scaled by 2^-4 (exact), which keeps the divisor below 2^124.
-  // (1 + e) / 16 comes out of one FMA bit-identical to the sum rounded and then scaled.
+  // exp and the reciprocal are the hardware approximations (relative error near 2^-22, far below half a
+  // bf16 step), spelled out rather than taken from __expf / __fdividef so that both run in their
+  // flush-to-zero forms (no extra range handling; neither flushes anything that matters here: a
+  // subnormal exp(-a) leaves 1 + exp(-a) = 1 either way, and the divisor below is never subnormal).
+  // An approximate division returns 0 for a divisor in (2^126, 2^128), which 1 + exp(-a) reaches for a in
+  // about (-88.7, -87.3) although the quotient there (about -5e-37) is still a normal bf16 value: both
+  // operands are therefore scaled by 2^-4 (exact; (1 + e) / 16 comes out of one FMA bit-identical to the
+  // sum rounded and then scaled), which keeps the divisor below 2^124.
   auto silu = [](float a) {
-    const float den16 = fmaf(__expf(-a), 0.0625f, 0.0625f);
-    return __fdividef(__fmul_rn(a, 0.0625f), den16);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(a, -1.4426950408889634f)));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e, 0.0625f, 0.0625f)));
+    return __fmul_rn(__fmul_rn(a, 0.0625f), r);
   };
   const float s0 = silu(a0), s1 = silu(a1);
   uint32_t s_pk;
