@@ -427,6 +427,7 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 // ------------------------------------------------------------------ host helpers
 namespace tnq_host {
 extern thread_local int g_last_cuda_error;
+bool tile_loads_evict_first();  // tuning switch TNQ_OPT_TILE_EVICT_FIRST (fp8_tensor.cu)
 int sm_count();  // SMs of the current device (cached per device)
 // single-launch path for tensors that fit in the GPU's shared memory (fp8_fused.cu)
 bool fused_plan(int64_t total_bytes, int* grid, uint32_t* slab_bytes);

@@ -413,6 +413,10 @@ static std::atomic<int> g_fused_small{1};
 static std::atomic<int> g_l2_keep_mb{64};
 static std::atomic<int> g_cast_l2_mode{0};
 static std::atomic<int> g_cast_pair{1};
+static std::atomic<int> g_tile_evict_first{0};  // measured: NVFP4 205.6 -> 209.5 us with it, MXFP8 one direction 31.3 -> 31.1
+namespace tnq_host {
+bool tile_loads_evict_first() { return g_tile_evict_first.load(std::memory_order_relaxed) != 0; }
+}  // namespace tnq_host
 // Walking backwards only pays once the tensor no longer fits in L2 as a whole.
 constexpr int64_t kReverseMinBytes = 96ll << 20;
 
@@ -432,6 +436,7 @@ extern "C" int tnq_set_option(int option, int value) {
     case TNQ_OPT_L2_KEEP_MB: g_l2_keep_mb.store(value < 0 ? 0 : value, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_CAST_L2_MODE: g_cast_l2_mode.store(value & 3, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_CAST_PAIR: g_cast_pair.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_TILE_EVICT_FIRST: g_tile_evict_first.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
     default: return TNQ_EINVAL;
   }
 }

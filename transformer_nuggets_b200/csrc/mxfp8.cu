@@ -381,8 +381,9 @@ __global__ void __launch_bounds__(512, 2)
 
 template <bool ROW, bool COL, int MODE>
 __global__ void __launch_bounds__((MxOp<ROW, COL, MODE>::kThreads), 2)
-    k_mxfp8(const __grid_constant__ CUtensorMap tmap, MxParams p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
-  run_tile_pipeline<MxOp<ROW, COL, MODE>>(&tmap, p, tiles_r, tiles_c, status);
+    k_mxfp8(const __grid_constant__ CUtensorMap tmap, MxParams p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status,
+            int evict_first) {
+  run_tile_pipeline<MxOp<ROW, COL, MODE>>(&tmap, p, tiles_r, tiles_c, status, evict_first != 0);
 }
 
 }  // namespace tnq
@@ -398,7 +399,8 @@ static int launch_mx(const CUtensorMap& map, const MxParams& p, uint32_t* status
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_mxfp8<ROW, COL, MODE><<<grid, kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
+  k_mxfp8<ROW, COL, MODE><<<grid, kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status,
+                                                                      tile_loads_evict_first() ? 1 : 0);
   return check_launch();
 }
 

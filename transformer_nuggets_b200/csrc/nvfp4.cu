@@ -149,8 +149,9 @@ struct Fp4Op {
 };
 
 __global__ void __launch_bounds__(Fp4Op::kThreads, 2)
-    k_nvfp4(const __grid_constant__ CUtensorMap tmap, Fp4Params p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
-  run_tile_pipeline<Fp4Op>(&tmap, p, tiles_r, tiles_c, status);
+    k_nvfp4(const __grid_constant__ CUtensorMap tmap, Fp4Params p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status,
+            int evict_first) {
+  run_tile_pipeline<Fp4Op>(&tmap, p, tiles_r, tiles_c, status, evict_first != 0);
 }
 
 }  // namespace tnq
@@ -186,7 +187,8 @@ extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int
   const int64_t tiles_r = (rows + kTileRows - 1) / kTileRows, tiles_c = (cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_nvfp4<<<grid, Fp4Op::kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
+  k_nvfp4<<<grid, Fp4Op::kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status,
+                                                             tile_loads_evict_first() ? 1 : 0);
   return check_launch();
 }
 

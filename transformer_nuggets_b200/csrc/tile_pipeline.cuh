@@ -56,9 +56,11 @@ struct TileCursor {
   }
 };
 
+// `evict_first`: the input tiles are loaded with an L2 evict-first policy (they are read exactly once).
 template <class Op>
 __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const typename Op::Params& p,
-                                                  uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
+                                                  uint32_t tiles_r, uint32_t tiles_c, uint32_t* status,
+                                                  bool evict_first = false) {
   extern __shared__ uint8_t tnq_dyn_smem[];
   uint8_t* const base = tile_smem_base(tnq_dyn_smem);
   uint64_t* const bars = reinterpret_cast<uint64_t*>(base + kStages * kTileBytes);
@@ -79,12 +81,16 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
   TileCursor cur, ahead;  // tile being consumed / next tile to load
   cur.init(first, gridDim.x, tiles_c);
   ahead = cur;
+  const uint64_t pol = l2_policy_evict_first();
+  auto load = [&](uint32_t s) {  // thread 0: arm stage s and load the tile at `ahead` into it
+    mbar_expect_tx(&bars[s], kTileBytes);
+    const int32_t x = (int32_t)(ahead.tc * kTileCols), y = (int32_t)(ahead.tr * kTileRows);
+    if (evict_first) tma_load_2d_hint(base + s * kTileBytes, tmap, x, y, &bars[s], pol);
+    else tma_load_2d(base + s * kTileBytes, tmap, x, y, &bars[s]);
+    ahead.advance();
+  };
   if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < (uint32_t)kStages && s < count; ++s) {
-      mbar_expect_tx(&bars[s], kTileBytes);
-      tma_load_2d(base + s * kTileBytes, tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s]);
-      ahead.advance();
-    }
+    for (uint32_t s = 0; s < (uint32_t)kStages && s < count; ++s) load(s);
   }
   uint32_t s = 0, phase = 0;
   for (uint32_t k = 0; k < count; ++k) {
@@ -98,11 +104,7 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
     if (full) Op::template process<true>(p, state, tile, sf, cur.tr, cur.tc);
     else Op::template process<false>(p, state, tile, sf, cur.tr, cur.tc);
     __syncthreads();  // tile fully consumed, scale staging complete
-    if (threadIdx.x == 0 && k + kStages < count) {
-      mbar_expect_tx(&bars[s], kTileBytes);
-      tma_load_2d(base + s * kTileBytes, tmap, (int32_t)(ahead.tc * kTileCols), (int32_t)(ahead.tr * kTileRows), &bars[s]);
-      ahead.advance();
-    }
+    if (threadIdx.x == 0 && k + kStages < count) load(s);
     Op::flush(p, sf, cur.tr, cur.tc);
     cur.advance();
     if (++s == (uint32_t)kStages) s = 0, phase ^= 1u;
