@@ -93,6 +93,9 @@ struct InTraits<TNQ_IN_BF16> {
     return m;
   }
   __device__ static __forceinline__ uint32_t fold(uint32_t m) { return fold_u16x2(m & 0x7fff7fffu) << 16; }  // -> fp32 bits
+  // both halves of an accumulator below the infinity pattern: everything it saw was finite
+  __device__ static __forceinline__ bool all_finite(uint32_t m) { return (((m & 0x7fff7fffu) + 0x00800080u) & 0x80008000u) == 0u; }
+  __device__ static __forceinline__ uint32_t merge(uint32_t m, uint32_t vm) { return absmax_bf16x2_1op(m, vm); }
   __device__ static __forceinline__ float load_scalar(const void* x, int64_t i) {
     return bf16bits_to_f32(reinterpret_cast<const uint16_t*>(x)[i]);
   }
@@ -107,24 +110,31 @@ struct InTraits<TNQ_IN_F32> {
     return m;
   }
   __device__ static __forceinline__ uint32_t fold(uint32_t m) { return m & 0x7fffffffu; }
+  __device__ static __forceinline__ bool all_finite(uint32_t m) { return (m & 0x7fffffffu) < 0x7f800000u; }
+  __device__ static __forceinline__ uint32_t merge(uint32_t m, uint32_t vm) { return absmax_f32_1op(m, vm); }
   __device__ static __forceinline__ float load_scalar(const void* x, int64_t i) {
     return reinterpret_cast<const float*>(x)[i];
   }
 };
 
-// 32 input bytes -> fp8 bytes, stored.
-template <int IN, int OUT, bool SAT>
+// 32 input bytes -> fp8 bytes, stored.  CHECKED = false skips the per-word NaN test: for callers that have
+// established that the vector and the scale are finite (saturated casts only: nothing can then be NaN).
+template <int IN, int OUT, bool SAT, bool CHECKED = true>
 __device__ __forceinline__ void quant_store(const Vec32B& v, float s, uint8_t* out, int64_t vec_index, bool hint,
                                             uint64_t policy) {
+  static_assert(CHECKED || SAT, "the unchecked conversion is for saturated casts");
   if constexpr (IN == TNQ_IN_BF16) {
-    const uint2 a = quant8_bf16<OUT, SAT>(make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), s);
-    const uint2 b = quant8_bf16<OUT, SAT>(make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]), s);
+    const uint4 lo4 = make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), hi4 = make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]);
+    uint2 a, b;
+    if constexpr (CHECKED) a = quant8_bf16<OUT, SAT>(lo4, s), b = quant8_bf16<OUT, SAT>(hi4, s);
+    else a = quant8_bf16_finite<OUT>(lo4, s), b = quant8_bf16_finite<OUT>(hi4, s);
     if (hint) stg128_hint(out + vec_index * 16, make_uint4(a.x, a.y, b.x, b.y), policy);
     else stg128(out + vec_index * 16, make_uint4(a.x, a.y, b.x, b.y));
   } else {
+    const uint4 lo4 = make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), hi4 = make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]);
     uint2 o;
-    o.x = quant4_f32<OUT, SAT>(make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]), s);
-    o.y = quant4_f32<OUT, SAT>(make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]), s);
+    if constexpr (CHECKED) o.x = quant4_f32<OUT, SAT>(lo4, s), o.y = quant4_f32<OUT, SAT>(hi4, s);
+    else o.x = quant4_f32_finite<OUT>(lo4, s), o.y = quant4_f32_finite<OUT>(hi4, s);
     if (hint) stg64_hint(out + vec_index * 8, o, policy);
     else stg64(out + vec_index * 8, o);
   }
@@ -136,21 +146,25 @@ template <int IN>
 struct GroupTraits {
   static constexpr int kVecs = (IN == TNQ_IN_BF16) ? 2 : 4;
 };
-template <int IN, int OUT, bool SAT>
+template <int IN, int OUT, bool SAT, bool CHECKED = true>
 __device__ __forceinline__ void quant_store_group(const Vec32B* v, float s, uint8_t* out, int64_t group_index, bool wide) {
+  static_assert(CHECKED || SAT, "the unchecked conversion is for saturated casts");
   uint32_t o[8];
   if constexpr (IN == TNQ_IN_BF16) {
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
-      const uint2 a = quant8_bf16<OUT, SAT>(make_uint4(v[k].w[0], v[k].w[1], v[k].w[2], v[k].w[3]), s);
-      const uint2 b = quant8_bf16<OUT, SAT>(make_uint4(v[k].w[4], v[k].w[5], v[k].w[6], v[k].w[7]), s);
+      const uint4 lo4 = make_uint4(v[k].w[0], v[k].w[1], v[k].w[2], v[k].w[3]), hi4 = make_uint4(v[k].w[4], v[k].w[5], v[k].w[6], v[k].w[7]);
+      uint2 a, b;
+      if constexpr (CHECKED) a = quant8_bf16<OUT, SAT>(lo4, s), b = quant8_bf16<OUT, SAT>(hi4, s);
+      else a = quant8_bf16_finite<OUT>(lo4, s), b = quant8_bf16_finite<OUT>(hi4, s);
       o[4 * k] = a.x, o[4 * k + 1] = a.y, o[4 * k + 2] = b.x, o[4 * k + 3] = b.y;
     }
   } else {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      o[2 * k] = quant4_f32<OUT, SAT>(make_uint4(v[k].w[0], v[k].w[1], v[k].w[2], v[k].w[3]), s);
-      o[2 * k + 1] = quant4_f32<OUT, SAT>(make_uint4(v[k].w[4], v[k].w[5], v[k].w[6], v[k].w[7]), s);
+      const uint4 lo4 = make_uint4(v[k].w[0], v[k].w[1], v[k].w[2], v[k].w[3]), hi4 = make_uint4(v[k].w[4], v[k].w[5], v[k].w[6], v[k].w[7]);
+      if constexpr (CHECKED) o[2 * k] = quant4_f32<OUT, SAT>(lo4, s), o[2 * k + 1] = quant4_f32<OUT, SAT>(hi4, s);
+      else o[2 * k] = quant4_f32_finite<OUT>(lo4, s), o[2 * k + 1] = quant4_f32_finite<OUT>(hi4, s);
     }
   }
   uint8_t* dst = out + group_index * 32;
@@ -259,6 +273,81 @@ __global__ void k_exchange_collect(ExchangeWait ex) {
 }
 
 // ---------------------------------------------------------------- cast (optionally + amax)
+// The streaming loop of k_cast.  A saturated cast skips the per-word NaN test (`fast`) for a vector when
+// nothing in it can become NaN: either everything is known to be finite (`known_finite`, uniform), or - with
+// the abs_max side output, where the vector's own maximum is at hand - that maximum and the scale are
+// finite.  Returns the thread's running |x| maximum (meaningful with AMAX; sign bits are meaningless).
+template <int IN, int OUT, bool SAT, bool AMAX, bool PAIR>
+__device__ __forceinline__ uint32_t cast_loop(const uint8_t* __restrict__ x, uint8_t* __restrict__ out, int64_t nvec, float s,
+                                              int reverse, int l2_mode, bool known_finite, bool scale_finite) {
+  using T = InTraits<IN>;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // reverse != 0 walks the tensor from its end: after an amax pass over the same tensor
+  // the most recently read (last) part is the part still in L2.
+  const int64_t first = reverse ? nvec - 1 : 0, dir = reverse ? -1 : 1;
+  // l2_mode bit 0: loads are last uses (evict first); bit 1: stores are never re-read (evict first)
+  const bool hint_ld = (l2_mode & 1) != 0, hint_st = (l2_mode & 2) != 0;
+  const uint64_t pol = l2_policy_evict_first();
+  uint32_t m = 0;
+  auto one_vector = [&](const Vec32B& v, int64_t j) {
+    bool fast = known_finite;
+    if constexpr (AMAX) {
+      const uint32_t vm = T::absmax(0u, v);
+      m = T::merge(m, vm);
+      fast = fast || (scale_finite && T::all_finite(vm));
+    }
+    if constexpr (SAT) {
+      if (fast) {
+        quant_store<IN, OUT, SAT, !SAT>(v, s, out, j, hint_st, pol);
+        return;
+      }
+    }
+    quant_store<IN, OUT, SAT>(v, s, out, j, hint_st, pol);
+  };
+  if constexpr (PAIR) {
+    constexpr int K = GroupTraits<IN>::kVecs;
+    const int64_t ngroup = nvec / K;
+    const bool wide = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
+    for (; i < ngroup; i += stride) {
+      const int64_t j = reverse ? ngroup - 1 - i : i;
+      Vec32B v[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) v[k] = ldg256(x + (j * K + k) * 32);
+      bool fast = known_finite;
+      if constexpr (AMAX) {
+        uint32_t vm = 0;
+#pragma unroll
+        for (int k = 0; k < K; ++k) vm = T::absmax(vm, v[k]);
+        m = T::merge(m, vm);
+        fast = fast || (scale_finite && T::all_finite(vm));
+      }
+      if (SAT && fast) quant_store_group<IN, OUT, SAT, !SAT>(v, s, out, j, wide);
+      else quant_store_group<IN, OUT, SAT>(v, s, out, j, wide);
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (unsigned)(nvec - ngroup * K)) {  // fewer than K vectors are left over
+      const int64_t j = ngroup * K + threadIdx.x;
+      one_vector(ldg256(x + j * 32), j);
+    }
+  } else {
+    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+      Vec32B v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint8_t* src = x + (first + dir * (i + u * stride)) * 32;
+        v[u] = hint_ld ? ldg256_hint(src, pol) : ldg256(src);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) one_vector(v[u], first + dir * (i + u * stride));
+    }
+    for (; i < nvec; i += stride) {
+      const int64_t j = first + dir * i;
+      one_vector(hint_ld ? ldg256_hint(x + j * 32, pol) : ldg256(x + j * 32), j);
+    }
+  }
+  return m;
+}
+
 // PAIR: a thread takes adjacent vectors per step (64 contiguous bytes of bf16 input) and writes their
 // 32 fp8 bytes with one 256-bit store; a warp then reads 2 KiB in one piece.  Used for the forward walk
 // over bf16 input (delayed-scale and plain casts: 72.0 -> 66.2 us at 16384 x 8192 with the abs_max side
@@ -290,57 +379,11 @@ __global__ void __launch_bounds__(kThreads)
   }
 
   const int64_t nvec = n / T::kElemsPerVec;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  // reverse != 0 walks the tensor from its end: after an amax pass over the same tensor
-  // the most recently read (last) part is the part still in L2.
-  const int64_t first = reverse ? nvec - 1 : 0, dir = reverse ? -1 : 1;
-  // l2_mode bit 0: loads are last uses (evict first); bit 1: stores are never re-read (evict first)
-  const bool hint_ld = (l2_mode & 1) != 0, hint_st = (l2_mode & 2) != 0;
-  const uint64_t pol = l2_policy_evict_first();
-  uint32_t m = 0;
-  if constexpr (PAIR) {
-    constexpr int K = GroupTraits<IN>::kVecs;
-    const int64_t ngroup = nvec / K;
-    const bool wide = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
-    for (; i < ngroup; i += stride) {
-      const int64_t j = reverse ? ngroup - 1 - i : i;
-      Vec32B v[K];
-#pragma unroll
-      for (int k = 0; k < K; ++k) v[k] = ldg256(x + (j * K + k) * 32);
-      if constexpr (AMAX) {
-#pragma unroll
-        for (int k = 0; k < K; ++k) m = T::absmax(m, v[k]);
-      }
-      quant_store_group<IN, OUT, SAT>(v, s, out, j, wide);
-    }
-    if (blockIdx.x == 0 && threadIdx.x < (unsigned)(nvec - ngroup * K)) {  // fewer than K vectors are left over
-      const int64_t j = ngroup * K + threadIdx.x;
-      const Vec32B v = ldg256(x + j * 32);
-      if constexpr (AMAX) m = T::absmax(m, v);
-      quant_store<IN, OUT, SAT>(v, s, out, j, false, pol);
-    }
-  } else {
-    for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
-      Vec32B v[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const uint8_t* src = x + (first + dir * (i + u * stride)) * 32;
-        v[u] = hint_ld ? ldg256_hint(src, pol) : ldg256(src);
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if constexpr (AMAX) m = T::absmax(m, v[u]);
-        quant_store<IN, OUT, SAT>(v[u], s, out, first + dir * (i + u * stride), hint_st, pol);
-      }
-    }
-    for (; i < nvec; i += stride) {
-      const int64_t j = first + dir * i;
-      const Vec32B v = hint_ld ? ldg256_hint(x + j * 32, pol) : ldg256(x + j * 32);
-      if constexpr (AMAX) m = T::absmax(m, v);
-      quant_store<IN, OUT, SAT>(v, s, out, j, hint_st, pol);
-    }
-  }
+  // A saturated cast whose scale is this tensor's own fp8_max / amax (the caller says so: l2_mode bit 2) and is
+  // finite and non-zero had a finite, non-zero amax: every element is finite and no product can be NaN.
+  const bool scale_finite = (__float_as_uint(s) & 0x7fffffffu) < 0x7f800000u;
+  const bool known_finite = SAT && (l2_mode & 4) != 0 && scale_finite && s != 0.0f;
+  uint32_t m = cast_loop<IN, OUT, SAT, AMAX, PAIR>(x, out, nvec, s, reverse, l2_mode, known_finite, scale_finite);
   if constexpr (AMAX) m = T::fold(m);
   if (blockIdx.x == 0) {
     for (int64_t j = nvec * T::kElemsPerVec + threadIdx.x; j < n; j += blockDim.x) {
@@ -518,7 +561,8 @@ static int cast_any(const void* x, void* out, int64_t n, int in_dtype, int out_d
   const int64_t in_bytes = n * (in_dtype == TNQ_IN_BF16 ? 2 : 4);
   const bool after_amax = pdl || scale_source == TNQ_SCALE_IS_AMAX;
   const int reverse = (after_amax && g_cast_reverse.load(std::memory_order_relaxed) && in_bytes > kReverseMinBytes) ? 1 : 0;
-  const int l2_mode = reverse ? g_cast_l2_mode.load(std::memory_order_relaxed) : 0;
+  // bit 2: the scale is this very tensor's fp8_max / amax (dynamic and sharded casts), see k_cast
+  const int l2_mode = (reverse ? g_cast_l2_mode.load(std::memory_order_relaxed) : 0) | ((pdl || ex.slots != nullptr) ? 4 : 0);
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* op = static_cast<uint8_t*>(out);
   Workspace* ws = static_cast<Workspace*>(workspace);
