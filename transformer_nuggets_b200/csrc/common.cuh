@@ -285,6 +285,15 @@ __device__ __forceinline__ uint32_t max_pk_bf16(uint32_t a, uint32_t b) {  // pe
   asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
+// per-half max(|a|, |b|) of two bf16 pairs in one instruction; the result's sign bits are the XOR of the
+// operands' and carry no meaning (mask with 0x7fff7fff before use).  Like max.bf16x2 it returns the other
+// operand when one is NaN (blocks that contain NaN are outside the block-scaled quantizers' contract).
+__device__ __forceinline__ uint32_t absmax_pk_bf16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // magnitude bits of a bf16 pair; the result orders like an unsigned integer per half
 __device__ __forceinline__ uint32_t mag_pk_bf16(uint32_t a) { return a & 0x7fff7fffu; }
 __device__ __forceinline__ uint32_t mul_pk_bf16(uint32_t a, uint32_t s) {  // per-half product, RNE

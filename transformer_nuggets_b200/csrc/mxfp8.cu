@@ -64,12 +64,12 @@ __device__ __forceinline__ void mx_row_pass(const MxParams& p, uint32_t tile, ui
   static_for<R / 2>([&](auto I) {
     constexpr int it = decltype(I)::value;
     const uint4 v = lds128_at<it * 512>(src);
-    uint32_t m = max_pk_bf16(max_pk_bf16(abs_pk_bf16(v.x), abs_pk_bf16(v.y)),
-                             max_pk_bf16(abs_pk_bf16(v.z), abs_pk_bf16(v.w)));
-    m = max_pk_bf16(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = max_pk_bf16(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    // max of magnitudes in one instruction per word (the sign bits of the result are meaningless)
+    uint32_t m = absmax_pk_bf16(absmax_pk_bf16(v.x, v.y), absmax_pk_bf16(v.z, v.w));
+    m = absmax_pk_bf16(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = absmax_pk_bf16(m, __shfl_xor_sync(0xffffffffu, m, 2));
     uint32_t byte, s2;
-    e8m0_from_amax<MODE>(fold_u16x2(m), byte, s2);
+    e8m0_from_amax<MODE>(fold_u16x2(m & 0x7fff7fffu), byte, s2);
     uint2 o;
     if (g_mixed_fma) {
       o.x = e4m3x4_scaled(v.x, v.y, (uint16_t)s2);
@@ -102,11 +102,11 @@ __device__ __forceinline__ void mx_col_compute(uint32_t tile, uint32_t sf_col, i
   static_for<32>([&](auto I) {
     constexpr int i = decltype(I)::value;
     v[i] = lds32_at<i * 256>(src);
-    m = max_pk_bf16(m, abs_pk_bf16(v[i]));
+    m = absmax_pk_bf16(m, v[i]);  // one instruction; sign bits of m are meaningless
   });
   uint32_t byte_lo, byte_hi, s_lo, s_hi;
-  e8m0_from_amax<MODE>(m & 0xffffu, byte_lo, s_lo);
-  e8m0_from_amax<MODE>(m >> 16, byte_hi, s_hi);
+  e8m0_from_amax<MODE>(m & 0x7fffu, byte_lo, s_lo);
+  e8m0_from_amax<MODE>((m >> 16) & 0x7fffu, byte_hi, s_hi);
   if (g_mixed_fma) {
     const uint16_t m_lo = (uint16_t)s_lo, m_hi = (uint16_t)s_hi;
 #pragma unroll

@@ -101,11 +101,10 @@ struct Fp4Op {
       const uint32_t src = tile + r * 256;
       const uint4 va = lds128(src + off_first);
       const uint4 vb = lds128(src + off_second);
-      uint32_t m = max_pk_bf16(max_pk_bf16(max_pk_bf16(mag_pk_bf16(va.x), mag_pk_bf16(va.y)),
-                                           max_pk_bf16(mag_pk_bf16(va.z), mag_pk_bf16(va.w))),
-                               max_pk_bf16(max_pk_bf16(mag_pk_bf16(vb.x), mag_pk_bf16(vb.y)),
-                                           max_pk_bf16(mag_pk_bf16(vb.z), mag_pk_bf16(vb.w))));
-      const float amax_b = bf16bits_to_f32(fold_u16x2(m));
+      // max of the sixteen magnitudes, one instruction per word (sign bits of m are meaningless until masked)
+      const uint32_t m = absmax_pk_bf16(absmax_pk_bf16(absmax_pk_bf16(va.x, va.y), absmax_pk_bf16(va.z, va.w)),
+                                        absmax_pk_bf16(absmax_pk_bf16(vb.x, vb.y), absmax_pk_bf16(vb.z, vb.w)));
+      const float amax_b = bf16bits_to_f32(fold_u16x2(m & 0x7fff7fffu));
       const float s = __fmul_rn(div6_bf16_valued(amax_b), g_enc);
       const uint32_t s_q = cvt_fp8x2<TNQ_FP8_E4M3>(s, 0.0f) & 0xffu;
       const float d = __fmul_rn(e4m3_to_f32(s_q), g_dec);
