@@ -1,0 +1,84 @@
+"""The selectable kernel variants behind one entry point produce the same bytes: direct-store and
+TMA-store forms of the row + column MXFP8 quantizer and of the transposing cast, and the tuning switches
+of the per-tensor cast.  Every variant is also compared with the oracle."""
+
+import pytest
+import torch
+
+import oracle
+import transformer_nuggets_b200 as tn
+from conftest import as_u8
+from transformer_nuggets_b200 import _lib
+from transformer_nuggets_b200.fp8 import scaled_quant, scaled_quant_transpose
+from transformer_nuggets_b200.workloads import make_input
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture
+def restore_defaults():
+    yield
+    _lib.call("tnq_mxfp8_set_store_variant", 1 + 4 * 1)
+    _lib.call("tnq_cast_transpose_set_store_variant", 1)
+    _lib.call("tnq_set_option", 5, 1)
+    _lib.call("tnq_set_option", 6, 0)
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (160, 256), (1024, 1056), (264, 64), (4096, 7168)])
+def test_mxfp8_store_variants_agree(shape, restore_defaults):
+    rows, cols = shape
+    rows -= rows % 32
+    x = make_input("mxfp8", "cpu", rows=rows, cols=cols)
+    wq, ws = oracle.mxfp8_quantize(x, "ceil")
+    wqt, wst = oracle.mxfp8_quantize(x.t().contiguous(), "ceil")
+    for code in (0, 1, 1 + 4 * 1, 1 + 4 * 2, 1 + 4 * 3):  # variant + 4 * (load / store eviction policy bits)
+        _lib.call("tnq_mxfp8_set_store_variant", code)
+        r = tn.quantize_mxfp8(x.to(DEV), columnwise=True, swizzle=True)
+        assert torch.equal(as_u8(r.q_row).cpu(), as_u8(wq)) and torch.equal(as_u8(r.q_col).cpu(), as_u8(wqt)), code
+        assert torch.equal(r.scale_row.cpu(), oracle.to_blocked(ws)) and torch.equal(r.scale_col.cpu(), oracle.to_blocked(wst)), code
+    with pytest.raises(_lib.TnqError):
+        _lib.call("tnq_mxfp8_set_store_variant", 2)
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (160, 264), (2048, 1024), (144, 200), (16, 8), (48, 4104), (130, 136)])
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_cast_transpose_variants_agree(shape, dtype, restore_defaults):
+    """Variant 1 (convert once, byte transpose, TMA store) and variant 0 (convert twice, direct stores);
+    (130, 136) has an out_t pitch that is not a multiple of 16 bytes and takes variant 0 either way."""
+    rows, cols = shape
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 30).to(torch.bfloat16)
+    x.view(-1)[3] = float("nan")
+    x.view(-1)[5] = float("-inf")
+    scale = torch.tensor([2.0])
+    for sat in (True, False):
+        want = as_u8(oracle.fp8_scaled_quant(x, scale, torch.zeros(1), dtype, sat))
+        for variant in (0, 1):
+            _lib.call("tnq_cast_transpose_set_store_variant", variant)
+            am = torch.zeros(1, device=DEV)
+            q, q_t = scaled_quant_transpose(x.to(DEV), scale.to(DEV), am, dtype, sat)
+            assert torch.equal(as_u8(q).cpu(), want) and torch.equal(as_u8(q_t).cpu(), want.t().contiguous()), (variant, sat)
+            assert torch.isnan(am).item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cast_pair_switch_agrees(dtype, restore_defaults):
+    """256-bit-store form of the forward per-tensor cast on and off, odd vector counts and a ragged tail included,
+    with and without the abs_max side output, NaN / inf inputs included."""
+    for n in (16 * 1000 + 7, 32 * 4096, 16 * 3 + 1, 5):
+        g = torch.Generator().manual_seed(n)
+        x = (torch.randn(n, generator=g) * 50).to(dtype)
+        if n > 40:
+            x[11] = float("nan")
+            x[29] = float("inf")
+        scale = torch.tensor([3.0])
+        for sat in (True, False):
+            want_am = torch.tensor([-1.0])
+            want = as_u8(oracle.fp8_scaled_quant(x, scale, want_am, torch.float8_e4m3fn, sat))
+            for on in (0, 1):
+                _lib.call("tnq_set_option", 5, on)
+                am = torch.tensor([-1.0], device=DEV)
+                q = scaled_quant(x.to(DEV), scale.to(DEV), am, torch.float8_e4m3fn, sat)
+                assert torch.equal(as_u8(q).cpu(), want), (n, sat, on)
+                assert torch.isnan(am).item() if n > 40 else am.item() == want_am.item()
