@@ -97,7 +97,9 @@ int tnq_fp8_amax(const void* x, int64_t n, int in_dtype, int out_dtype, void* wo
  * fp8_max / max(*scale, 1e-12) (TNQ_SCALE_IS_AMAX).  saturated != 0 clamps to
  * +-fp8_max first; saturated == 0 overflows to NaN (e4m3) / inf (e5m2) exactly as
  * a non-saturating RNE cast does.  If abs_max_inout is non-null it becomes
- * max(*abs_max_inout, max|x|) and `workspace` must be given.
+ * max(*abs_max_inout, max|x|) - an atomic max on the bit patterns compared as signed integers,
+ * so a NaN already stored stays and a negative starting value (-1.0, say) loses; `workspace`
+ * must then be given (reserved: the current kernel does not touch it).
  * Replaces `scaled_cast` / `scaled_quant` (fp8/scaled_quant.py:6-32, 35-75) with
  * the overflow semantics of `eager_scaled_quant` (:78-102). */
 int tnq_fp8_scaled_cast(const void* x, void* out, int64_t n, int in_dtype, int out_dtype,
