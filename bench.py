@@ -777,6 +777,9 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _lib.call("tnq_mxfp8_set_store_variant", int(os.environ["TNQ_MX_STORE_VARIANT"]))
     if os.environ.get("TNQ_CT_STORE_VARIANT"):
         _lib.call("tnq_cast_transpose_set_store_variant", int(os.environ["TNQ_CT_STORE_VARIANT"]))
+    for item in filter(None, os.environ.get("TNQ_SET_OPTIONS", "").split(",")):  # "option=value,..." -> tnq_set_option
+        opt, val = item.split("=")
+        _lib.call("tnq_set_option", int(opt), int(val))
 
     def report(name, ms, note, bytes_per_elem=None):
         cfg = CONFIGS[name]

@@ -84,6 +84,18 @@ int tnq_abi_version(void);
  * their input tiles with an L2 evict-first policy.  (The row + column MXFP8 quantizer and the
  * transposing cast always do: it pays there, here it measured 2 % slower for NVFP4.) */
 #define TNQ_OPT_TILE_EVICT_FIRST 6
+/* TNQ_OPT_FUSED_LAUNCH (default 1): how the single-launch dynamic cast (tensors up to ~33.5 MB) is
+ * launched.  1 = plain launch of at most one CTA per SM, chained like the other kernels (see
+ * TNQ_OPT_PDL_CHAIN); if other streams keep SMs busy for longer than the kernel's bounded wait (about a
+ * second) the call reports TNQ_ETIMEOUT in the workspace's status word.  0 = cooperative launch: the
+ * driver guarantees that all CTAs are resident together whatever else runs, and the chained launch is
+ * honoured only inside CUDA graphs (about 2 us more per eager call). */
+#define TNQ_OPT_FUSED_LAUNCH 7
+/* TNQ_OPT_PDL_CHAIN (default 1): the quantizer kernels are launched with programmatic stream
+ * serialization: a kernel's CTAs are placed and set up while the stream's previous kernel drains
+ * (they wait for it before they touch memory), which hides the launch latency between
+ * back-to-back calls.  0 = plain stream order. */
+#define TNQ_OPT_PDL_CHAIN 8
 int tnq_set_option(int option, int value);
 
 /* amax = max|x| over n elements, written as fp32 to ws word TNQ_WS_AMAX_WORD and,

@@ -82,3 +82,97 @@ def test_cast_pair_switch_agrees(dtype, restore_defaults):
                 q = scaled_quant(x.to(DEV), scale.to(DEV), am, torch.float8_e4m3fn, sat)
                 assert torch.equal(as_u8(q).cpu(), want), (n, sat, on)
                 assert torch.isnan(am).item() if n > 40 else am.item() == want_am.item()
+
+
+@pytest.fixture
+def restore_launch_defaults():
+    yield
+    _lib.call("tnq_set_option", 7, 1)
+    _lib.call("tnq_set_option", 8, 1)
+
+
+def test_launch_modes_agree(restore_launch_defaults):
+    """Single-launch dynamic cast launched plain or cooperatively, every kernel chained to the stream's previous
+    kernel or in plain stream order: the same bytes, equal to the oracle's, and a clean status word."""
+    x = make_input("fp8_tensor", "cpu", rows=1024, cols=4096)
+    want = as_u8(oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)[0])
+    xd = x.to(DEV)
+    for coop, chain in ((0, 0), (0, 1), (1, 0), (1, 1)):
+        _lib.call("tnq_set_option", 7, coop)
+        _lib.call("tnq_set_option", 8, chain)
+        outs = [tn.dynamic_scaled_quant(xd) for _ in range(6)]  # back to back: each call overlaps the previous one's tail
+        r = tn.quantize_mxfp8(xd, columnwise=True, swizzle=True)
+        tn.check_status(xd.device, "launch modes")
+        for q in outs:
+            assert torch.equal(as_u8(q).cpu(), want), (coop, chain)
+        wq, _ = oracle.mxfp8_quantize(x, "ceil")
+        assert torch.equal(as_u8(r.q_row).cpu(), as_u8(wq)), (coop, chain)
+    with pytest.raises(_lib.TnqError):
+        _lib.call("tnq_set_option", 7, 2)
+
+
+def test_chained_launch_sees_the_previous_kernels_output():
+    """A chained kernel starts while the stream's previous kernel drains and must not read its input early:
+    the input buffer is rewritten by a torch kernel right before every cast (torch kernel -> cast), the cast's
+    output feeds the next kernel of ours (amax -> cast, quantize -> swizzle), twenty times without a host sync."""
+    g = torch.Generator().manual_seed(5)
+    src = [(torch.randn(2048, 4096, generator=g) * (i + 1)).to(torch.bfloat16) for i in range(4)]
+    src_d = [s.to(DEV) for s in src]
+    x = torch.empty_like(src_d[0])
+    big = torch.empty(8192, 4096, dtype=torch.bfloat16, device=DEV)  # 64 MiB: the two-launch path
+    outs, outs_big, swz = [], [], []
+    for i in range(20):
+        x.copy_(src_d[i % 4])
+        outs.append(tn.dynamic_scaled_quant(x))
+        big.copy_(src_d[i % 4].repeat(4, 1))
+        outs_big.append(tn.dynamic_scaled_quant(big))
+        r = tn.quantize_mxfp8(x, swizzle=False)
+        swz.append((r.scale_row, tn.to_blocked(r.scale_row)))
+    tn.check_status(x.device, "chained launches")
+    want = []
+    for s in src:
+        want.append(as_u8(oracle.fp8_dynamic_quant(s, torch.float8_e4m3fn)[0]))
+    for i in range(20):
+        assert torch.equal(as_u8(outs[i]).cpu(), want[i % 4]), i
+        assert torch.equal(as_u8(outs_big[i]).cpu(), want[i % 4].repeat(4, 1)), i
+        assert torch.equal(swz[i][1].cpu(), oracle.to_blocked(swz[i][0].cpu())), i
+
+
+def test_single_launch_casts_on_two_streams():
+    """Two host threads cast on two streams at once, each with its own workspace: every call's CTAs are placed
+    together although the launches are not cooperative, so no call runs into the bounded wait of its exchange."""
+    import threading
+
+    x = make_input("fp8_tensor", "cpu")
+    want = as_u8(oracle.fp8_dynamic_quant(x, torch.float8_e4m3fn)[0])
+    dev = torch.device(DEV, torch.cuda.current_device())
+    xd = x.to(dev)
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def worker(k):
+        try:
+            s = torch.cuda.Stream(device=dev)
+            ws = torch.zeros(_lib.WORKSPACE_BYTES // 4, dtype=torch.int32, device=dev)
+            outs = [torch.empty_like(xd, dtype=torch.float8_e4m3fn) for _ in range(4)]
+            s.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(s):
+                for i in range(200):
+                    _lib.call("tnq_fp8_dynamic_cast", xd.data_ptr(), outs[i % 4].data_ptr(), xd.numel(), _lib.IN_BF16,
+                              _lib.FP8_E4M3, ws.data_ptr(), 0, s.cuda_stream)
+            s.synchronize()
+            results[k] = (outs, int(ws[_lib.WS_STATUS_WORD]))
+        except Exception as e:  # pragma: no cover - reported below
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for k in range(2):
+        outs, status = results[k]
+        assert status == 0, (k, status)
+        for q in outs:
+            assert torch.equal(as_u8(q).cpu(), want), k

@@ -451,4 +451,24 @@ inline int check_launch() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TNQ_OK : cuda_fail(e);
 }
+// Chained launch (TNQ_OPT_PDL_CHAIN, fp8_tensor.cu): the kernel is launched with programmatic stream
+// serialization, so its CTAs are placed and run their prologue (barrier setup, descriptor prefetch)
+// while the stream's previous kernel drains; every kernel launched this way executes
+// griddepcontrol.wait before it touches global memory and releases its own successor right after.
+bool pdl_chain();
+template <typename... KArgs, typename... Args>
+inline int launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_chain() ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  return e == cudaSuccess ? TNQ_OK : cuda_fail(e);
+}
 }  // namespace tnq_host

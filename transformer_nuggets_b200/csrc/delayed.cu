@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(128)
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= tensors) return;
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   uint32_t* h = reinterpret_cast<uint32_t*>(history) + (int64_t)t * len;
   const uint32_t newest = __float_as_uint(amax[t]) & 0x7fffffffu;
   uint32_t keep[kDelayedMaxHistory / 32];
@@ -60,8 +62,8 @@ extern "C" int tnq_delayed_scale_update(float* amax_history, float* amax, float*
   const int warps = 4;
   const unsigned grid = (unsigned)((tensors + warps - 1) / warps);
   if (out_dtype == TNQ_FP8_E4M3)
-    tnq::k_delayed_scale_update<TNQ_FP8_E4M3><<<grid, warps * 32, 0, stream>>>(amax_history, amax, scale, (int)tensors, history_len);
-  else
-    tnq::k_delayed_scale_update<TNQ_FP8_E5M2><<<grid, warps * 32, 0, stream>>>(amax_history, amax, scale, (int)tensors, history_len);
-  return tnq_host::check_launch();
+    return tnq_host::launch_chained(tnq::k_delayed_scale_update<TNQ_FP8_E4M3>, dim3(grid), dim3(warps * 32), 0, stream, amax_history,
+                                    amax, scale, (int)tensors, history_len);
+  return tnq_host::launch_chained(tnq::k_delayed_scale_update<TNQ_FP8_E5M2>, dim3(grid), dim3(warps * 32), 0, stream, amax_history,
+                                  amax, scale, (int)tensors, history_len);
 }

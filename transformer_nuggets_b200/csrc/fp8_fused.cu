@@ -2,7 +2,7 @@
 // memory of the whole GPU (148 SMs x ~226 KB = 33.5 MB: a 4096 x 4096 bf16 tensor
 // just fits).
 //
-// One CTA per SM, launched cooperatively so that all CTAs are resident.  Each CTA
+// One CTA per SM, all resident together (see launch_fused for how that is ensured).  Each CTA
 // owns a contiguous slab of the tensor and brings it into shared memory with bulk
 // async copies (cp.async.bulk, 32 KiB pieces, one mbarrier each, all in flight at
 // once).  As pieces land the CTA folds |x| maxima; a grid-wide exchange (one max, one
@@ -35,7 +35,7 @@ struct FusedWorkspace {
 };
 static_assert(sizeof(FusedWorkspace) == TNQ_WORKSPACE_BYTES, "workspace layout");
 
-// All CTAs of the cooperative grid meet here and leave with the maximum of their contributions.
+// All CTAs of the grid meet here and leave with the maximum of their contributions.
 // Thread 0 of every CTA: a max into the high word of this call's pair, a fence, an increment of the
 // low word (which wraps to zero when the last CTA arrives), then it polls the pair with ONE 64-bit
 // load until the low word reads zero - the same load delivers the maximum.  Measured beside a
@@ -99,7 +99,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
   uint8_t* slab = base + kFusedHeaderBytes;
   const uint32_t slab_s = smem_u32(slab);
   unsigned long long t_start = 0, t_loaded = 0, t_exchanged = 0, g_start = 0, g_loaded = 0, g_exchanged = 0;
-  if constexpr (PROF) t_start = clock64(), g_start = globaltimer_ns();
 
   const int64_t begin = (int64_t)blockIdx.x * slab_bytes;
   int64_t my_bytes64 = total_bytes - begin;
@@ -113,6 +112,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     fence_mbar_init();
   }
   __syncthreads();
+  // launched with programmatic stream serialization the CTA may get here while the previous kernel of the
+  // stream still runs: everything that reads what that kernel wrote (the input, the workspace) stays behind this
+  pdl_wait();
+  pdl_launch_dependents();
+  if constexpr (PROF) t_start = clock64(), g_start = globaltimer_ns();  // the stream's previous kernel has finished
   uint32_t gen = 0;
   if (threadIdx.x == 0) {
     for (int p = 0; p < pieces; ++p) {
@@ -207,6 +211,8 @@ using namespace tnq_host;
 
 namespace tnq_host {
 
+int fused_launch_mode();  // fp8_tensor.cu, TNQ_OPT_FUSED_LAUNCH
+
 struct FusedLimits {
   int sms = 0;
   int max_smem = 0;
@@ -245,11 +251,28 @@ static int launch_fused(const uint8_t* x, uint8_t* out, int64_t total_bytes, int
   cfg.blockDim = dim3(kFusedThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
+  // The grid never exceeds one CTA per SM, so a plain launch places every CTA as soon as the SMs are free, and
+  // the block scheduler hands out all CTAs of one grid before it turns to the next grid: the CTAs of a call
+  // meet in the exchange without the cooperative attribute.  What the attribute adds is a guarantee when
+  // other streams hold SMs; without it a call whose CTAs cannot all be placed within the exchange's bound
+  // (about a second) reports TNQ_ETIMEOUT in the status word instead of waiting.  What it costs is the
+  // chained launch: the runtime honours programmatic stream serialization on a cooperative launch only inside
+  // a CUDA graph (measured per call at 4096 x 4096: cooperative 14.4 us eager / 12.6 us replayed, plain +
+  // chained 12.5 us / 12.6 us).  TNQ_OPT_FUSED_LAUNCH picks: 1 = plain (default), 0 = cooperative.
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (fused_launch_mode() == 0) {
+    attr[na].id = cudaLaunchAttributeCooperative;
+    attr[na].val.cooperative = 1;
+    ++na;
+  }
+  if (pdl_chain()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, k_dynamic_fused<IN, OUT, PROF>, x, out, total_bytes, slab_bytes,
                                      static_cast<FusedWorkspace*>(ws), scale_out, stamps);
   return e == cudaSuccess ? TNQ_OK : cuda_fail(e);

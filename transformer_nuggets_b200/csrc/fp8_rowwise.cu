@@ -108,6 +108,8 @@ __global__ void __launch_bounds__(kRowThreads)
     }
   };
   Vec32B v[VPT], vn[kPrefetch ? VPT : 1];
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   load_row(v, blockIdx.x);
   for (int64_t step = blockIdx.x; step < n_steps; step += gridDim.x) {
     const int64_t r = step * kGroups + g;
@@ -233,6 +235,8 @@ __global__ void __launch_bounds__(kRowThreads)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   if (threadIdx.x == 0)
     for (int64_t k = 0; k < stages && k < count; ++k) issue(k);
 
@@ -317,6 +321,8 @@ __global__ void __launch_bounds__(kRowThreads)
                    float* __restrict__ s52) {
   using T = RowIn<IN>;
   __shared__ uint32_t smem32[33];
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const uint8_t* xr = x + r * nvec_row * 32;
     uint32_t m = 0;
@@ -371,8 +377,7 @@ static int launch_rowwise(const uint8_t* x, int64_t rows, int64_t cols, int nvec
   const int64_t steps = (rows + kGroups - 1) / kGroups;
   const int64_t cap = row_resident_ctas<k_rowwise<IN, G, VPT>>();
   const int grid = (int)(steps < cap ? steps : cap);
-  k_rowwise<IN, G, VPT><<<grid, kRowThreads, 0, stream>>>(x, rows, cols, nvec_row, q43, s43, q52, s52);
-  return check_launch();
+  return launch_chained(k_rowwise<IN, G, VPT>, dim3(grid), dim3(kRowThreads), 0, stream, x, rows, cols, nvec_row, q43, s43, q52, s52);
 }
 
 template <int IN, int G>
@@ -421,8 +426,8 @@ static int launch_rowwise_tma(const uint8_t* x, int64_t rows, int64_t cols, int 
   const int64_t steps = (rows + kGroups - 1) / kGroups;
   const int64_t cap = (int64_t)per_sm * sm_count();
   const int grid = (int)(steps < cap ? steps : cap);
-  k_rowwise_tma<IN, G, UPT><<<grid, kRowThreads, smem, stream>>>(x, rows, cols, nunit_row, stages, q43, s43, q52, s52, status);
-  return check_launch();
+  return launch_chained(k_rowwise_tma<IN, G, UPT>, dim3(grid), dim3(kRowThreads), smem, stream, x, rows, cols, nunit_row, stages, q43,
+                        s43, q52, s52, status);
 }
 
 template <int IN, int G>
@@ -453,8 +458,7 @@ static int rowwise_in(const uint8_t* x, int64_t rows, int64_t cols, uint8_t* q43
   if (nvec_row > 4 * 256) {
     const int64_t cap = row_resident_ctas<k_rowwise_long<IN>>();
     const int grid = (int)(rows < cap ? rows : cap);
-    k_rowwise_long<IN><<<grid, kRowThreads, 0, stream>>>(x, rows, cols, nvec_row, q43, s43, q52, s52);
-    return check_launch();
+    return launch_chained(k_rowwise_long<IN>, dim3(grid), dim3(kRowThreads), 0, stream, x, rows, cols, nvec_row, q43, s43, q52, s52);
   }
   const int nv = (int)nvec_row;
   // largest group that still gives every thread a vector: more threads per row means fewer

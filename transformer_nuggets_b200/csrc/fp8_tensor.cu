@@ -209,6 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint32_t m = 0;
+  pdl_wait();  // chained launch: the input may come from the stream's previous kernel
   if (keep_from < nvec) {
     // A cast pass over the same tensor follows and walks it from the end: ask L2 to
     // hold on to the tail (vectors >= keep_from) and to let go of the rest first.
@@ -359,6 +360,7 @@ __global__ void __launch_bounds__(kThreads)
   using T = InTraits<IN>;
   __shared__ uint32_t smem32[33];
   pdl_wait();  // the scale may come from the preceding amax launch
+  pdl_launch_dependents();
   float s;
   if (ex.slots != nullptr) {  // amax of all ranks, read from this GPU's own slots
     __shared__ float s_amax;
@@ -457,7 +459,11 @@ static std::atomic<int> g_l2_keep_mb{64};
 static std::atomic<int> g_cast_l2_mode{0};
 static std::atomic<int> g_cast_pair{1};
 static std::atomic<int> g_tile_evict_first{0};  // measured: NVFP4 205.6 -> 209.5 us with it, MXFP8 one direction 31.3 -> 31.1
+static std::atomic<int> g_fused_launch{1};
+static std::atomic<int> g_pdl_chain{1};
 namespace tnq_host {
+bool pdl_chain() { return g_pdl_chain.load(std::memory_order_relaxed) != 0; }
+int fused_launch_mode() { return g_fused_launch.load(std::memory_order_relaxed); }
 bool tile_loads_evict_first() { return g_tile_evict_first.load(std::memory_order_relaxed) != 0; }
 }  // namespace tnq_host
 // Walking backwards only pays once the tensor no longer fits in L2 as a whole.
@@ -480,6 +486,11 @@ extern "C" int tnq_set_option(int option, int value) {
     case TNQ_OPT_CAST_L2_MODE: g_cast_l2_mode.store(value & 3, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_CAST_PAIR: g_cast_pair.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_TILE_EVICT_FIRST: g_tile_evict_first.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_PDL_CHAIN: g_pdl_chain.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_FUSED_LAUNCH:
+      if (value != 0 && value != 1) return TNQ_EINVAL;
+      g_fused_launch.store(value, std::memory_order_relaxed);
+      return TNQ_OK;
     default: return TNQ_EINVAL;
   }
 }
@@ -505,7 +516,7 @@ static int launch(int64_t n_vec, cudaStream_t stream, bool pdl, Args... args) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = (pdl || pdl_chain()) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, Kernel, args...);
   return e == cudaSuccess ? TNQ_OK : cuda_fail(e);
 }

@@ -126,6 +126,8 @@ __global__ void __launch_bounds__(512, 2)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {  // every thread keeps `ahead` kStages tiles in front of `cur`
     if (threadIdx.x == 0 && s < count) issue(s);
     ahead.advance();
@@ -185,8 +187,8 @@ static int launch_cast_transpose(const CUtensorMap& map, const CastTParams& p, u
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_cast_transpose<OUT, SAT><<<grid, 512, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
-  return check_launch();
+  return launch_chained(k_cast_transpose<OUT, SAT>, dim3(grid), dim3(512), kTileSmemBytes, stream, map, p, (uint32_t)tiles_r,
+                        (uint32_t)tiles_c, status);
 }
 
 namespace tnq {
@@ -241,6 +243,8 @@ __global__ void __launch_bounds__(512, 2)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   for (uint32_t s = 0; s < (uint32_t)kBtStages; ++s) {
     if (t == 0 && s < count) issue(s);
     ahead.advance();
@@ -338,8 +342,8 @@ static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_cast_transpose_bt<OUT, SAT><<<grid, 512, kBtSmemBytes, stream>>>(map, map_col, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
-  return check_launch();
+  return launch_chained(k_cast_transpose_bt<OUT, SAT>, dim3(grid), dim3(512), kBtSmemBytes, stream, map, map_col, p,
+                        (uint32_t)tiles_r, (uint32_t)tiles_c, status);
 }
 
 template <int OUT, bool SAT>

@@ -177,6 +177,8 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
   const uint32_t xs = smem_u32(tnq_gemv_smem) + kGemvWarps * S * kSlotBytes;             // x as f16x2 (whole warps)
   const uint32_t fx = xs + gemv_x_bytes<FP4>(k);                                         // x block factors (fp32)
   const uint32_t kb = k / F::kBlock;
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
 
   // ---- prologue: decode x once per CTA.  Piece q of chunk c is stored at uint4 index
   // (c / 32) * 32 * Q + q * 32 + (c % 32), so that the 32 lanes of a warp read consecutive
@@ -401,10 +403,9 @@ static int launch_gemv(const void* x, const void* w, const void* x_sf, const voi
   const int64_t want = (groups + kGemvWarps - 1) / kGemvWarps;
   const int64_t cap = (int64_t)per_sm * sm_count();
   const int grid = (int)(want < cap ? want : cap);
-  k_blockscaled_gemv<FP4><<<grid, kGemvThreads, smem, stream>>>(
-      static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(x_sf),
-      static_cast<const uint8_t*>(w_sf), xg, wg, (uint32_t)n, (uint32_t)k, layout, static_cast<uint16_t*>(y));
-  return check_launch();
+  return launch_chained(k_blockscaled_gemv<FP4>, dim3(grid), dim3(kGemvThreads), smem, stream, static_cast<const uint8_t*>(w),
+                        static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(x_sf), static_cast<const uint8_t*>(w_sf), xg,
+                        wg, (uint32_t)n, (uint32_t)k, layout, static_cast<uint16_t*>(y));
 }
 
 extern "C" int tnq_mxfp8_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, int64_t n, int64_t k,

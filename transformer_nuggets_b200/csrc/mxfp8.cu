@@ -238,6 +238,8 @@ __global__ void __launch_bounds__(512, 2)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   // every thread keeps `ahead` kStages tiles in front of `cur`; thread 0 also issues the first loads
   for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
     if (threadIdx.x == 0 && s < count) issue(s);
@@ -325,6 +327,8 @@ __global__ void __launch_bounds__(512, 2)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   for (uint32_t s = 0; s < (uint32_t)kStagesTs; ++s) {
     if (threadIdx.x == 0 && s < count) issue(s);
     ahead.advance();
@@ -399,9 +403,8 @@ static int launch_mx(const CUtensorMap& map, const MxParams& p, uint32_t* status
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_mxfp8<ROW, COL, MODE><<<grid, kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status,
-                                                                      tile_loads_evict_first() ? 1 : 0);
-  return check_launch();
+  return launch_chained(k_mxfp8<ROW, COL, MODE>, dim3(grid), dim3(kThreads), kTileSmemBytes, stream, map, p, (uint32_t)tiles_r,
+                        (uint32_t)tiles_c, status, tile_loads_evict_first() ? 1 : 0);
 }
 
 template <int MODE>
@@ -411,8 +414,8 @@ static int launch_mx_dual(const CUtensorMap& map, const MxParams& p, uint32_t* s
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_mxfp8_dual<MODE><<<grid, 512, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status);
-  return check_launch();
+  return launch_chained(k_mxfp8_dual<MODE>, dim3(grid), dim3(512), kTileSmemBytes, stream, map, p, (uint32_t)tiles_r,
+                        (uint32_t)tiles_c, status);
 }
 
 // variant: 0 = both passes store straight to global memory, 1 = transposed payload through shared
@@ -437,9 +440,8 @@ static int launch_mx_dual_ts(const CUtensorMap& map, const MxParams& p, uint32_t
   const int64_t tiles_r = (p.rows + kTileRows - 1) / kTileRows, tiles_c = (p.cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_mxfp8_dual_ts<MODE><<<grid, 512, kTsSmemBytes, stream>>>(map, map_col, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status,
-                                                             g_mx_tuning.load(std::memory_order_relaxed));
-  return check_launch();
+  return launch_chained(k_mxfp8_dual_ts<MODE>, dim3(grid), dim3(512), kTsSmemBytes, stream, map, map_col, p, (uint32_t)tiles_r,
+                        (uint32_t)tiles_c, status, g_mx_tuning.load(std::memory_order_relaxed));
 }
 
 template <int MODE>

@@ -186,9 +186,8 @@ extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int
   const int64_t tiles_r = (rows + kTileRows - 1) / kTileRows, tiles_c = (cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  k_nvfp4<<<grid, Fp4Op::kThreads, kTileSmemBytes, stream>>>(map, p, (uint32_t)tiles_r, (uint32_t)tiles_c, status,
-                                                             tile_loads_evict_first() ? 1 : 0);
-  return check_launch();
+  return launch_chained(k_nvfp4, dim3(grid), dim3(Fp4Op::kThreads), kTileSmemBytes, stream, map, p, (uint32_t)tiles_r,
+                        (uint32_t)tiles_c, status, tile_loads_evict_first() ? 1 : 0);
 }
 
 // ---------------------------------------------------------------- code packing
@@ -196,6 +195,8 @@ namespace tnq {
 // codes[rows, cols] (one e2m1 code per byte, 0..15) -> packed[rows, cols/2],
 // byte = code[2i] | code[2i+1] << 4.  Each thread packs 16 codes into 8 bytes.
 __global__ void __launch_bounds__(256) k_pack_fp4(const uint8_t* __restrict__ codes, uint8_t* __restrict__ packed, int64_t n16) {
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
     const uint4 v = ldg128(codes + i * 16);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -222,6 +223,6 @@ extern "C" int tnq_pack_fp4_codes(const void* codes, int64_t rows, int64_t cols,
   int64_t blocks = (n16 + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  tnq::k_pack_fp4<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(codes), static_cast<uint8_t*>(packed), n16);
-  return check_launch();
+  return launch_chained(tnq::k_pack_fp4, dim3((unsigned)blocks), dim3(256), 0, stream, static_cast<const uint8_t*>(codes),
+                        static_cast<uint8_t*>(packed), n16);
 }

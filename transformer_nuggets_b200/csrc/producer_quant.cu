@@ -160,6 +160,8 @@ __global__ void __launch_bounds__(kNormThreads, (PROD == kProdRmsNorm && KIND ==
   };
   Vec32B v[VPT], vn[kPrefetch ? VPT : 1];
   Vec32B bv[kB], bn[(kPrefetch && PROD == kProdSwiGlu) ? VPT : 1];
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   load_row(v, bv, blockIdx.x);
   for (int64_t step = blockIdx.x; step < n_steps; step += gridDim.x) {
     const int64_t r = step * kGroups + g;
@@ -337,8 +339,8 @@ static int launch_norm(const uint8_t* x, const uint8_t* w, float eps, int64_t ro
   }
   const int64_t steps = (rows + kGroups - 1) / kGroups;
   const int grid = (int)(steps < cached[dev] ? steps : cached[dev]);
-  k_producer_quant<G, VPT, KIND, PROD, WRITE_Y><<<grid, kNormThreads, 0, stream>>>(x, w, eps, rows, cols, nvec_row, out);
-  return check_launch();
+  return launch_chained(k_producer_quant<G, VPT, KIND, PROD, WRITE_Y>, dim3(grid), dim3(kNormThreads), 0, stream, x, w, eps, rows,
+                        cols, nvec_row, out);
 }
 
 template <int G, int VPT, int KIND, int PROD>

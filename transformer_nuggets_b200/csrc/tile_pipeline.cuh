@@ -77,6 +77,8 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   typename Op::State state = Op::init(p);
   TileCursor cur, ahead;  // tile being consumed / next tile to load
   cur.init(first, gridDim.x, tiles_c);

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256)
   __shared__ __align__(16) uint8_t s[4096];
   const int64_t rb = blockIdx.y;
   const int64_t cb0 = (int64_t)blockIdx.x * 8;
+  pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
+  pdl_launch_dependents();
   for (int idx = threadIdx.x; idx < 4096; idx += 256) {
     const int r = idx >> 5, c = idx & 31;
     const int64_t gr = rb * 128 + r, gc = cb0 * 4 + c;
@@ -38,6 +40,6 @@ extern "C" int tnq_to_blocked(const void* in, int64_t rows, int64_t cols, void* 
   const int64_t nrb = (rows + 127) / 128, ncb = (cols + 3) / 4;
   if (nrb > 65535) return TNQ_EUNSUPPORTED;
   dim3 grid((unsigned)((ncb + 7) / 8), (unsigned)nrb);
-  tnq::k_to_blocked<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(in), rows, cols, static_cast<uint8_t*>(out), ncb);
-  return tnq_host::check_launch();
+  return tnq_host::launch_chained(tnq::k_to_blocked, grid, dim3(256), 0, stream, static_cast<const uint8_t*>(in), rows, cols,
+                                  static_cast<uint8_t*>(out), ncb);
 }
