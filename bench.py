@@ -1315,7 +1315,29 @@ def _bench_mxfp8(dev, res, timed, report, ws, stream):
         torch.equal(qr[:1024].cpu(), wq.view(torch.uint8)) and torch.equal(qc[:1024].cpu(), wqt.view(torch.uint8))
         and torch.equal(sr[:n_row].cpu(), oracle.to_blocked(wsr)) and torch.equal(sc[:n_col].cpu(), oracle.to_blocked(wsc)))
     res["mxfp8_rowwise_only"] = report("mxfp8", timed(f3r, [None]), "row-wise output only", 2.0 + 1.0 + 1.0 / 32)
-    del x, qr, qc
+    del qr, qc
+    # the same tile pipeline with the arithmetic taken out: TMA load of a 128 x 128 tile, TMA store of the same bytes
+    y = torch.empty_like(x)
+    best = None
+    for stages, per_sm in ((2, 2), (3, 1), (3, 2), (2, 3)):
+        def fc(_, stages=stages, per_sm=per_sm):
+            _lib.call("tnq_tile_copy", x.data_ptr(), y.data_ptr(), rows, cols, stages, per_sm, status, stream)
+        try:
+            ms = timed(fc, [None])
+        except _lib.TnqError:
+            continue
+        if best is None or ms < best[0]:
+            best = (ms, stages, per_sm)
+    if best is not None:
+        ok = bool(torch.equal(y[-256:], x[-256:]))
+        res["tile_copy_ceiling"] = {
+            "us": best[0] * 1e3, "GBps": 4.0 * rows * cols / (best[0] * 1e-3) / 1e9, "stages": best[1], "ctas_per_sm": best[2],
+            "copied_correctly": ok,
+            "note": "TMA tile load -> TMA tile store of the same 8192 x 7168 bf16 matrix, no arithmetic (4 B/elem): what a "
+                    "tile pipeline reaches on this shape; best of four stage / occupancy settings"}
+        per_byte = best[0] / (4.0 * rows * cols)
+        res["mxfp8"]["frac_of_tile_copy"] = per_byte * 4.0625 * rows * cols / (res["mxfp8"]["us"] * 1e-3)
+    del x, y
 
 
 def _bench_nvfp4(dev, res, timed, report, ws, stream):

@@ -229,12 +229,21 @@ int tnq_fp8_dynamic_cast(const void* x, void* out, int64_t n, int in_dtype, int 
 /* Diagnostic twin of tnq_fp8_dynamic_cast (bf16 -> e4m3, single-launch path only, else
  * TNQ_EUNSUPPORTED): the same kernel built with time stamps, for splitting its duration into
  * phases.  stamps: device buffer of 8 uint64 per CTA (256 CTAs at most); words 0..3 are SM
- * clock readings at kernel entry / slab loaded and CTA maximum known / grid-wide exchange
+ * clock readings when the CTA is past its wait for the stream's previous kernel / slab loaded and CTA maximum known / grid-wide exchange
  * done / last store issued, words 4..7 the global nanosecond timer at the same four points.
  * *grid_out (host, nullable) receives the number of CTAs.
  * No counterpart in the reference. */
 int tnq_fp8_dynamic_cast_profile(const void* x, void* out, int64_t n, void* workspace, float* scale_out,
                                  unsigned long long* stamps, int* grid_out, tnq_stream_t stream);
+
+/* Diagnostic: copies a row-major [rows, cols] bf16 matrix (rows, cols multiples of 128) through the
+ * block-scaled quantizers' tile pipeline with the arithmetic taken out: 2-D TMA load of a 128 x 128
+ * tile into a ring of `stages` (2..6) shared-memory stages, 2-D TMA store of the same bytes,
+ * `ctas_per_sm` (1..4) persistent CTAs per SM.  Its time is the practical floor of a kernel that reads
+ * and writes that many bytes tile by tile; bench.py reports the quantizers against it.
+ * TNQ_EUNSUPPORTED if the stages do not fit that many CTAs.  No counterpart in the reference. */
+int tnq_tile_copy(const void* x, void* y, int64_t rows, int64_t cols, int stages, int ctas_per_sm,
+                  uint32_t* status, tnq_stream_t stream);
 
 /* The same cast as tnq_fp8_dynamic_cast for callers that cannot provide (or create)
  * device scratch: plug-ins that receive only tensors and a stream from their host

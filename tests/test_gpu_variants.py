@@ -176,3 +176,22 @@ def test_single_launch_casts_on_two_streams():
         assert status == 0, (k, status)
         for q in outs:
             assert torch.equal(as_u8(q).cpu(), want), k
+
+
+@pytest.mark.parametrize("shape,stages,per_sm", [((128, 128), 2, 1), ((1024, 896), 2, 2), ((2048, 4096), 3, 2), ((512, 256), 6, 1)])
+def test_tile_copy_diagnostic(shape, stages, per_sm):
+    """The arithmetic-free twin of the tile pipeline copies every byte; shapes that are not whole tiles and
+    stage counts that do not fit are refused before any launch."""
+    g = torch.Generator().manual_seed(shape[0] + shape[1])
+    x = torch.randn(*shape, generator=g).to(torch.bfloat16).to(DEV)
+    y = torch.zeros_like(x)
+    ws = _lib.workspace(x.device)
+    status = ws.data_ptr() + 4 * _lib.WS_STATUS_WORD
+    for _ in range(3):
+        _lib.call("tnq_tile_copy", x.data_ptr(), y.data_ptr(), shape[0], shape[1], stages, per_sm, status, _lib.stream_ptr(x.device))
+    tn.check_status(x.device, "tile copy")
+    assert torch.equal(as_u8(x), as_u8(y))
+    with pytest.raises(_lib.TnqError):
+        _lib.call("tnq_tile_copy", x.data_ptr(), y.data_ptr(), shape[0] - 1, shape[1], stages, per_sm, status, _lib.stream_ptr(x.device))
+    with pytest.raises(_lib.TnqError):
+        _lib.call("tnq_tile_copy", x.data_ptr(), y.data_ptr(), shape[0], shape[1], 6, 4, status, _lib.stream_ptr(x.device))

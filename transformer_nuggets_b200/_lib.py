@@ -38,6 +38,7 @@ SIGNATURES = {
     "tnq_fp8_scaled_cast": [_p, _p, _i64, _i, _i, _p, _i, _i, _p, _p, _p],
     "tnq_fp8_dynamic_cast": [_p, _p, _i64, _i, _i, _p, _p, _p],
     "tnq_fp8_dynamic_cast_profile": [_p, _p, _i64, _p, _p, _p, _p, _p],
+    "tnq_tile_copy": [_p, _p, _i64, _i64, _i, _i, _p, _p],
     "tnq_fp8_dynamic_cast_static": [_p, _p, _i64, _i, _i, _p, _p],
     "tnq_fp8_dynamic_cast_static_max_elements": [],
     "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p],

@@ -21,7 +21,7 @@ CSRC = os.path.join(PKG, "csrc")
 OBJ_DIR = os.path.join(ROOT, "build", "tnq")
 LIB_PATH = os.path.join(CSRC, "libtnq.so")
 
-SOURCES = ["fp8_tensor.cu", "fp8_fused.cu", "fp8_rowwise.cu", "mxfp8.cu", "nvfp4.cu", "to_blocked.cu", "exchange.cu", "gemv.cu", "delayed.cu", "fp8_transpose.cu", "producer_quant.cu", "fp8_gemm.cu", "mxfp8_gemm.cu", "nvfp4_gemm.cu"]
+SOURCES = ["fp8_tensor.cu", "fp8_fused.cu", "fp8_rowwise.cu", "mxfp8.cu", "nvfp4.cu", "to_blocked.cu", "exchange.cu", "gemv.cu", "delayed.cu", "fp8_transpose.cu", "tile_copy.cu", "producer_quant.cu", "fp8_gemm.cu", "mxfp8_gemm.cu", "nvfp4_gemm.cu"]
 HEADERS = ["common.cuh", "tile_pipeline.cuh", "mx_scale.cuh", os.path.join(ROOT, "include", "tnq.h")]
 
 NVCC_FLAGS = [
