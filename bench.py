@@ -852,10 +852,8 @@ def _bench_transpose(dev, res, timed, peak, ws, stream):
                   _lib.SCALE_IS_SCALE, 1, am.data_ptr(), q.data_ptr(), q_t.data_ptr(), status, stream)
 
     def dynamic(_):
-        _lib.call("tnq_fp8_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), 0, stream)
-        _lib.call("tnq_fp8_cast_transpose", x.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_E4M3,
-                  ws.data_ptr() + 4 * _lib.WS_SCALE_WORD, _lib.SCALE_IS_SCALE, 1, 0, q.data_ptr(), q_t.data_ptr(), status,
-                  stream)
+        _lib.call("tnq_fp8_dynamic_cast_transpose", x.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(),
+                  q.data_ptr(), q_t.data_ptr(), 0, stream)
 
     res["fp8_cast_transpose"] = report(timed(delayed, [None]), 4.0,
                                        f"{rows}x{cols}, delayed scale + abs_max side output, both layouts from one read")
@@ -1355,9 +1353,8 @@ def _bench_nvfp4(dev, res, timed, report, ws, stream):
     amax_ptr = ws.data_ptr() + 4 * _lib.WS_AMAX_WORD
 
     def f4(_):
-        _lib.call("tnq_fp8_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), 0, stream)
-        _lib.call("tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, amax_ptr, packed.data_ptr(), sf.data_ptr(),
-                  _lib.SCALES_SWIZZLED, gs.data_ptr(), status, stream)
+        _lib.call("tnq_nvfp4_quantize_dynamic", x.data_ptr(), rows, cols, _lib.IN_BF16, ws.data_ptr(), packed.data_ptr(),
+                  sf.data_ptr(), _lib.SCALES_SWIZZLED, gs.data_ptr(), stream)
 
     def f4s(_):
         _lib.call("tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, amax_ptr, packed.data_ptr(), sf.data_ptr(),

@@ -145,6 +145,13 @@ int tnq_delayed_scale_update(float* amax_history, float* amax, float* scale, int
 int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
                            const float* scale, int scale_kind, int saturated, float* abs_max_inout,
                            void* out, void* out_t, uint32_t* status, tnq_stream_t stream);
+
+/* Dynamic-scale form of tnq_fp8_cast_transpose: amax pass into the workspace, then the saturated cast in
+ * both layouts with scale = fp8_max / max(amax, 1e-12), tiles walked from the end of the matrix as in
+ * tnq_nvfp4_quantize_dynamic.  *scale_out (nullable) receives the scale; status = word 3 of the workspace. */
+int tnq_fp8_dynamic_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
+                                   void* workspace, void* out, void* out_t, float* scale_out,
+                                   tnq_stream_t stream);
 /* Tuning switch for the transposing cast, same results either way.  1 (default): every element is
  * converted once, the fp8 bytes are transposed in shared memory and out_t is written by TMA stores
  * (rows % 16 == 0, else variant 0 runs); 0: both outputs converted separately and stored straight to
@@ -314,6 +321,14 @@ int tnq_mxfp8_set_store_variant(int variant);
 int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype,
                        const float* global_amax, void* packed, void* sf, int scale_layout,
                        float* global_scale_out, uint32_t* status, tnq_stream_t stream);
+
+/* The same with the tensor-wide amax taken first (dynamic global scale): an amax pass into the workspace
+ * (word 1), then the quantizer, which walks the tiles from the END of the matrix - the part the amax pass
+ * read last and asked L2 to keep - so that part is not read from HBM a second time (16384 x 16384: 202 ->
+ * 192 us for the pair).  x additionally 32-byte aligned; the status word is word 3 of the workspace. */
+int tnq_nvfp4_quantize_dynamic(const void* x, int64_t rows, int64_t cols, int in_dtype, void* workspace,
+                               void* packed, void* sf, int scale_layout, float* global_scale_out,
+                               tnq_stream_t stream);
 
 /* codes[rows, cols] (one e2m1 code 0..15 per byte) -> packed[rows, cols/2] with
  * byte = code[2i] | code[2i+1] << 4.  Requires cols % 16 == 0.

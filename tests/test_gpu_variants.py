@@ -195,3 +195,39 @@ def test_tile_copy_diagnostic(shape, stages, per_sm):
         _lib.call("tnq_tile_copy", x.data_ptr(), y.data_ptr(), shape[0] - 1, shape[1], stages, per_sm, status, _lib.stream_ptr(x.device))
     with pytest.raises(_lib.TnqError):
         _lib.call("tnq_tile_copy", x.data_ptr(), y.data_ptr(), shape[0], shape[1], 6, 4, status, _lib.stream_ptr(x.device))
+
+
+def test_dynamic_entries_match_their_two_call_forms():
+    """tnq_nvfp4_quantize_dynamic and tnq_fp8_dynamic_cast_transpose (amax pass + tiles walked from the end of the
+    matrix) give the bytes of the amax call followed by the plain entry point (tiles walked from the start),
+    on a matrix larger than L2 and on ragged small ones."""
+    dev = torch.device(DEV, torch.cuda.current_device())
+    ws = _lib.workspace(dev)
+    stream = _lib.stream_ptr(dev)
+    status = ws.data_ptr() + 4 * _lib.WS_STATUS_WORD
+    for rows, cols in ((8192, 8192), (160, 272), (128, 128), (32, 16)):
+        g = torch.Generator().manual_seed(rows + cols)
+        x = (torch.randn(rows, cols, generator=g) * 3).to(torch.bfloat16).to(dev)
+        r = tn.quantize_nvfp4(x)  # dynamic entry
+        packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev)
+        sf = torch.empty_like(r.block_scales.view(torch.uint8))
+        gs = torch.empty(1, dtype=torch.float32, device=dev)
+        _lib.call("tnq_fp8_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), 0, stream)
+        _lib.call("tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, ws.data_ptr() + 4 * _lib.WS_AMAX_WORD,
+                  packed.data_ptr(), sf.data_ptr(), _lib.SCALES_SWIZZLED, gs.data_ptr(), status, stream)
+        assert torch.equal(r.packed.view(torch.uint8), packed) and torch.equal(r.block_scales.view(torch.uint8), sf)
+        assert torch.equal(r.global_scale, gs)
+        if cols % 8 == 0:
+            q, q_t, scale = tn.fp8.dynamic_scaled_quant_transpose(x)
+            want, want_scale = oracle.fp8_dynamic_quant(x.cpu(), torch.float8_e4m3fn)
+            assert torch.equal(as_u8(q).cpu(), as_u8(want)) and torch.equal(as_u8(q_t).cpu(), as_u8(want).t().contiguous())
+            assert torch.equal(scale.cpu(), want_scale)
+    tn.check_status(dev, "dynamic entries")
+    x = torch.zeros(128, 128, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(128 * 128, dtype=torch.uint8, device=dev)
+    with pytest.raises(_lib.TnqError):  # no workspace
+        _lib.call("tnq_nvfp4_quantize_dynamic", x.data_ptr(), 128, 128, _lib.IN_BF16, 0, out.data_ptr(), out.data_ptr(),
+                  _lib.SCALES_SWIZZLED, 0, stream)
+    with pytest.raises(_lib.TnqError):
+        _lib.call("tnq_fp8_dynamic_cast_transpose", x.data_ptr(), 128, 128, _lib.IN_BF16, _lib.FP8_E4M3, 0, out.data_ptr(),
+                  out.data_ptr(), 0, stream)

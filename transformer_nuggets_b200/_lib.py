@@ -47,6 +47,7 @@ SIGNATURES = {
     "tnq_mxfp8_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "tnq_mxfp8_set_store_variant": [_i],
     "tnq_nvfp4_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p, _p],
+    "tnq_nvfp4_quantize_dynamic": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p],
     "tnq_pack_fp4_codes": [_p, _i64, _i64, _p, _p],
     "tnq_to_blocked": [_p, _i64, _i64, _p, _p],
     "tnq_exchange_create": [_p, _p],
@@ -57,6 +58,7 @@ SIGNATURES = {
     "tnq_fp8_sharded_cast": [_p, _p, _i64, _i, _i, _p, _p, _i, _i, ctypes.c_uint32, _p, _p],
     "tnq_sharded_amax": [_p, _i64, _i, _p, _p, _i, _i, ctypes.c_uint32, _p, _p],
     "tnq_fp8_cast_transpose": [_p, _i64, _i64, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p],
+    "tnq_fp8_dynamic_cast_transpose": [_p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p],
     "tnq_cast_transpose_set_store_variant": [_i],
     "tnq_rmsnorm_fp8_rowwise": [_p, _p, ctypes.c_float, _i64, _i64, _p, _p, _p, _p],
     "tnq_rmsnorm_mxfp8": [_p, _p, ctypes.c_float, _i64, _i64, _p, _p, _i, _i, _p, _p],

@@ -437,6 +437,11 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 namespace tnq_host {
 extern thread_local int g_last_cuda_error;
 bool tile_loads_evict_first();  // tuning switch TNQ_OPT_TILE_EVICT_FIRST (fp8_tensor.cu)
+// Tensor-wide amax pass of the per-tensor cast (fp8_tensor.cu) into the workspace (amax bits in word 1, fp8_max / amax
+// in word 2; the latter also to *scale_out when given).  tail_stays: a pass that walks the same tensor from its end
+// follows; tensors that exceed L2 are then read with the policy that keeps their last TNQ_OPT_L2_KEEP_MB in L2.
+int amax_pass(const void* x, int64_t n, int in_dtype, void* workspace, float* scale_out, float fp8_max, cudaStream_t stream,
+              bool tail_stays);
 int sm_count();  // SMs of the current device (cached per device)
 // single-launch path for tensors that fit in the GPU's shared memory (fp8_fused.cu)
 bool fused_plan(int64_t total_bytes, int* grid, uint32_t* slab_bytes);

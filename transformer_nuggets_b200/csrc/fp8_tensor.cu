@@ -530,6 +530,14 @@ static int amax_launch(const uint8_t* xp, int64_t n, int in_dtype, Workspace* ws
   return launch<k_amax<TNQ_IN_F32, false>>(n / 8, stream, false, xp, n, ws, amax_out, scale_out, fmax, none, keep);
 }
 
+namespace tnq_host {
+int amax_pass(const void* x, int64_t n, int in_dtype, void* workspace, float* scale_out, float fp8_max, cudaStream_t stream,
+              bool tail_stays) {
+  return amax_launch(static_cast<const uint8_t*>(x), n, in_dtype, static_cast<Workspace*>(workspace), nullptr, scale_out,
+                     fp8_max, stream, tail_stays);
+}
+}  // namespace tnq_host
+
 extern "C" int tnq_fp8_amax(const void* x, int64_t n, int in_dtype, int out_dtype, void* workspace,
                             float* amax_out, tnq_stream_t stream) {
   int rc = check_common(x, n, in_dtype, out_dtype);

@@ -209,7 +209,7 @@ constexpr int kBtSmemBytes = 2 * kStageOutBytes + kBtStages * kTileBytes + 64;
 template <int OUT, bool SAT>
 __global__ void __launch_bounds__(512, 2)
     k_cast_transpose_bt(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap map_col, CastTParams p,
-                        uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
+                        uint32_t tiles_r, uint32_t tiles_c, uint32_t* status, int backwards) {
   extern __shared__ __align__(1024) uint8_t tnq_dyn_smem_1k[];
   uint8_t* const base = tnq_dyn_smem_1k;
   const uint32_t stg_t = smem_u32(base);  // transposed staging, read by the TMA store
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(512, 2)
   const uint64_t pol = l2_policy_evict_first();
 
   TileCursor cur, ahead;
-  cur.init(first, gridDim.x, tiles_c);
+  cur.init(first, gridDim.x, tiles_c, backwards ? ntiles - 1 : 0);
   ahead = cur;
   auto issue = [&](uint32_t s) {
     mbar_expect_tx(&bars[s], kTileBytes);
@@ -333,7 +333,8 @@ extern "C" int tnq_cast_transpose_set_store_variant(int v) {
 }
 
 template <int OUT, bool SAT>
-static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
+static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream,
+                                    bool backwards) {
   const int cap = resident_ctas_smem<k_cast_transpose_bt<OUT, SAT>, 512, kBtSmemBytes>();
   if (cap < 1) return cuda_fail(cudaGetLastError());
   CUtensorMap map_col;
@@ -343,19 +344,22 @@ static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
   return launch_chained(k_cast_transpose_bt<OUT, SAT>, dim3(grid), dim3(512), kBtSmemBytes, stream, map, map_col, p,
-                        (uint32_t)tiles_r, (uint32_t)tiles_c, status);
+                        (uint32_t)tiles_r, (uint32_t)tiles_c, status, backwards && ntiles > 1 ? 1 : 0);
 }
 
 template <int OUT, bool SAT>
-static int launch_cast_transpose_any(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
+static int launch_cast_transpose_any(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream,
+                                     bool backwards) {
   if (g_ct_store_variant.load(std::memory_order_relaxed) == 1 && p.rows % 16 == 0 && aligned16(p.out_t))
-    return launch_cast_transpose_bt<OUT, SAT>(map, p, status, stream);
+    return launch_cast_transpose_bt<OUT, SAT>(map, p, status, stream, backwards);
   return launch_cast_transpose<OUT, SAT>(map, p, status, stream);
 }
 
-extern "C" int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
-                                      const float* scale, int scale_kind, int saturated, float* abs_max_inout,
-                                      void* out, void* out_t, uint32_t* status, tnq_stream_t stream) {
+// amax_workspace != null: the dynamic form - an amax pass into that workspace first (the scale is then read from its
+// word 2), and the tiles walked from the end of the matrix, the part that pass read last and asked L2 to keep.
+static int cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype, const float* scale,
+                          int scale_kind, int saturated, float* abs_max_inout, void* out, void* out_t, uint32_t* status,
+                          cudaStream_t stream, void* amax_workspace, float* scale_out) {
   if (rows < 0 || cols < 0) return TNQ_EINVAL;
   if (in_dtype != TNQ_IN_BF16) return TNQ_EUNSUPPORTED;
   if (out_dtype != TNQ_FP8_E4M3 && out_dtype != TNQ_FP8_E5M2) return TNQ_EINVAL;
@@ -376,9 +380,32 @@ extern "C" int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols,
   p.abs_max = abs_max_inout;
   p.out = static_cast<uint8_t*>(out), p.out_t = static_cast<uint8_t*>(out_t);
   p.t_aligned = (rows % 32 == 0) && ((reinterpret_cast<uintptr_t>(out_t) & 31u) == 0);
+  const bool dynamic = amax_workspace != nullptr;
+  if (dynamic) {
+    rc = amax_pass(x, rows * cols, in_dtype, amax_workspace, scale_out, out_dtype == TNQ_FP8_E4M3 ? 448.0f : 57344.0f, stream,
+                   true);
+    if (rc != TNQ_OK) return rc;
+  }
   if (out_dtype == TNQ_FP8_E4M3)
-    return saturated ? launch_cast_transpose_any<TNQ_FP8_E4M3, true>(map, p, status, stream)
-                     : launch_cast_transpose_any<TNQ_FP8_E4M3, false>(map, p, status, stream);
-  return saturated ? launch_cast_transpose_any<TNQ_FP8_E5M2, true>(map, p, status, stream)
-                   : launch_cast_transpose_any<TNQ_FP8_E5M2, false>(map, p, status, stream);
+    return saturated ? launch_cast_transpose_any<TNQ_FP8_E4M3, true>(map, p, status, stream, dynamic)
+                     : launch_cast_transpose_any<TNQ_FP8_E4M3, false>(map, p, status, stream, dynamic);
+  return saturated ? launch_cast_transpose_any<TNQ_FP8_E5M2, true>(map, p, status, stream, dynamic)
+                   : launch_cast_transpose_any<TNQ_FP8_E5M2, false>(map, p, status, stream, dynamic);
+}
+
+extern "C" int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
+                                      const float* scale, int scale_kind, int saturated, float* abs_max_inout,
+                                      void* out, void* out_t, uint32_t* status, tnq_stream_t stream) {
+  return cast_transpose(x, rows, cols, in_dtype, out_dtype, scale, scale_kind, saturated, abs_max_inout, out, out_t, status,
+                        stream, nullptr, nullptr);
+}
+
+extern "C" int tnq_fp8_dynamic_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
+                                              void* workspace, void* out, void* out_t, float* scale_out,
+                                              tnq_stream_t stream) {
+  if (workspace == nullptr) return TNQ_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(x) & 31u) != 0) return TNQ_EALIGN;  // the amax pass reads 256-bit vectors
+  uint32_t* words = static_cast<uint32_t*>(workspace);
+  return cast_transpose(x, rows, cols, in_dtype, out_dtype, reinterpret_cast<const float*>(words + 2), TNQ_SCALE_IS_SCALE, 1,
+                        nullptr, out, out_t, words + 3, stream, workspace, scale_out);
 }

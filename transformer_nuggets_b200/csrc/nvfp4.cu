@@ -149,8 +149,8 @@ struct Fp4Op {
 
 __global__ void __launch_bounds__(Fp4Op::kThreads, 2)
     k_nvfp4(const __grid_constant__ CUtensorMap tmap, Fp4Params p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status,
-            int evict_first) {
-  run_tile_pipeline<Fp4Op>(&tmap, p, tiles_r, tiles_c, status, evict_first != 0);
+            int walk) {  // bit 0: evict-first loads, bit 1: tiles from the end of the matrix
+  run_tile_pipeline<Fp4Op>(&tmap, p, tiles_r, tiles_c, status, (walk & 1) != 0, (walk & 2) != 0);
 }
 
 }  // namespace tnq
@@ -158,9 +158,9 @@ __global__ void __launch_bounds__(Fp4Op::kThreads, 2)
 using namespace tnq;
 using namespace tnq_host;
 
-extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype,
-                                  const float* global_amax, void* packed, void* sf, int scale_layout,
-                                  float* global_scale_out, uint32_t* status, tnq_stream_t stream) {
+static int nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype, const float* global_amax, void* packed,
+                          void* sf, int scale_layout, float* global_scale_out, uint32_t* status, cudaStream_t stream,
+                          void* amax_workspace) {
   if (rows < 0 || cols < 0) return TNQ_EINVAL;
   if (in_dtype != TNQ_IN_BF16) return TNQ_EUNSUPPORTED;
   if (scale_layout != TNQ_SCALES_RAW && scale_layout != TNQ_SCALES_SWIZZLED) return TNQ_EINVAL;
@@ -186,8 +186,32 @@ extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int
   const int64_t tiles_r = (rows + kTileRows - 1) / kTileRows, tiles_c = (cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
+  // dynamic global scale: the amax pass first, then the tiles from the end of the matrix, which is the part the amax
+  // pass read last and asked L2 to keep (16384 x 16384: 202 -> 192 us for the two launches)
+  const bool dynamic = amax_workspace != nullptr;
+  if (dynamic) {
+    rc = amax_pass(x, rows * cols, in_dtype, amax_workspace, nullptr, 448.0f, stream, true);
+    if (rc != TNQ_OK) return rc;
+  }
   return launch_chained(k_nvfp4, dim3(grid), dim3(Fp4Op::kThreads), kTileSmemBytes, stream, map, p, (uint32_t)tiles_r,
-                        (uint32_t)tiles_c, status, tile_loads_evict_first() ? 1 : 0);
+                        (uint32_t)tiles_c, status, (tile_loads_evict_first() ? 1 : 0) | (dynamic && ntiles > 1 ? 2 : 0));
+}
+
+extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype,
+                                  const float* global_amax, void* packed, void* sf, int scale_layout,
+                                  float* global_scale_out, uint32_t* status, tnq_stream_t stream) {
+  return nvfp4_quantize(x, rows, cols, in_dtype, global_amax, packed, sf, scale_layout, global_scale_out, status, stream,
+                        nullptr);
+}
+
+extern "C" int tnq_nvfp4_quantize_dynamic(const void* x, int64_t rows, int64_t cols, int in_dtype, void* workspace,
+                                          void* packed, void* sf, int scale_layout, float* global_scale_out,
+                                          tnq_stream_t stream) {
+  if (workspace == nullptr) return TNQ_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(x) & 31u) != 0) return TNQ_EALIGN;  // the amax pass reads 256-bit vectors
+  uint32_t* words = static_cast<uint32_t*>(workspace);
+  return nvfp4_quantize(x, rows, cols, in_dtype, reinterpret_cast<const float*>(words + 1), packed, sf, scale_layout,
+                        global_scale_out, words + 3, stream, workspace);
 }
 
 // ---------------------------------------------------------------- code packing

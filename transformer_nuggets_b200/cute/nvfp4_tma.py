@@ -71,20 +71,20 @@ def quantize_nvfp4(x: torch.Tensor, global_amax: torch.Tensor | None = None, *, 
     gscale = torch.empty(1, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         stream = _lib.stream_ptr(dev)
+        layout = _lib.SCALES_SWIZZLED if swizzle else _lib.SCALES_RAW
         if global_amax is None:
-            _lib.call("tnq_fp8_amax", x.data_ptr(), x.numel(), _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(), 0, stream)
-            amax_ptr = ws.data_ptr() + 4 * _lib.WS_AMAX_WORD
+            if rows and cols:  # amax pass + quantizer in one call (the quantizer re-reads the end of x from L2)
+                _lib.call("tnq_nvfp4_quantize_dynamic", x.data_ptr(), rows, cols, _lib.IN_BF16, ws.data_ptr(),
+                          packed.data_ptr(), sf.data_ptr(), layout, gscale.data_ptr(), stream)
         else:
             _lib.require_cuda(global_amax, "global_amax")
             if global_amax.dtype != torch.float32 or global_amax.numel() != 1:
                 raise TypeError("global_amax must be one fp32 element")
-            amax_ptr = global_amax.data_ptr()
-        if rows and cols:
-            _lib.call(
-                "tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, amax_ptr, packed.data_ptr(),
-                sf.data_ptr(), _lib.SCALES_SWIZZLED if swizzle else _lib.SCALES_RAW, gscale.data_ptr(),
-                ws.data_ptr() + 4 * _lib.WS_STATUS_WORD, stream,
-            )
+            if rows and cols:
+                _lib.call(
+                    "tnq_nvfp4_quantize", x.data_ptr(), rows, cols, _lib.IN_BF16, global_amax.data_ptr(), packed.data_ptr(),
+                    sf.data_ptr(), layout, gscale.data_ptr(), ws.data_ptr() + 4 * _lib.WS_STATUS_WORD, stream,
+                )
     return NVFP4Result(packed.view(torch.float4_e2m1fn_x2), sf, gscale)
 
 

@@ -159,16 +159,10 @@ def dynamic_scaled_quant_transpose(inpt_tensor: torch.Tensor, fp8_dtype: torch.d
     out_t = torch.empty(cols, rows, dtype=fp8_dtype, device=dev)
     scale = torch.empty(1, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        ws = _lib.workspace(dev)
-        stream = _lib.stream_ptr(dev)
-        _lib.call("tnq_fp8_amax", inpt_tensor.data_ptr(), inpt_tensor.numel(), _lib.IN_BF16, _lib.FP8_DTYPES[fp8_dtype],
-                  ws.data_ptr(), 0, stream)
         _lib.call(
-            "tnq_fp8_cast_transpose", inpt_tensor.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_DTYPES[fp8_dtype],
-            ws.data_ptr() + 4 * _lib.WS_SCALE_WORD, _lib.SCALE_IS_SCALE, 1, 0, out.data_ptr(), out_t.data_ptr(),
-            ws.data_ptr() + 4 * _lib.WS_STATUS_WORD, stream,
+            "tnq_fp8_dynamic_cast_transpose", inpt_tensor.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_DTYPES[fp8_dtype],
+            _lib.workspace(dev).data_ptr(), out.data_ptr(), out_t.data_ptr(), scale.data_ptr(), _lib.stream_ptr(dev),
         )
-        scale.copy_(ws[_lib.WS_SCALE_WORD:_lib.WS_SCALE_WORD + 1].view(torch.float32))
     return out, out_t, scale
 
 
