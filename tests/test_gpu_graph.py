@@ -91,3 +91,37 @@ def test_rowwise_and_blockscaled_graph():
     wp, wsf, wg = oracle.nvfp4_quantize(xc)
     assert torch.equal(packed.cpu(), wp) and torch.equal(sf.cpu(), as_u8(wsf)) and torch.equal(gs.cpu(), wg)
     assert int(ws[_lib.WS_STATUS_WORD].item()) == 0
+
+
+def test_dynamic_tile_entries_graph():
+    """The one-call dynamic NVFP4 quantizer and the dynamic transposing cast captured in a graph and replayed
+    on changed input (chained launches inside the graph: each node starts behind its predecessor)."""
+    x = make_input("mxfp8", DEV, rows=1024, cols=2048)
+    rows, cols = x.shape
+    packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=DEV)
+    sf = torch.empty(512 * (rows // 128) * (cols // 64), dtype=torch.uint8, device=DEV)
+    gs = torch.empty(1, dtype=torch.float32, device=DEV)
+    q = torch.empty(rows, cols, dtype=torch.uint8, device=DEV)
+    q_t = torch.empty(cols, rows, dtype=torch.uint8, device=DEV)
+    scale = torch.empty(1, dtype=torch.float32, device=DEV)
+    ws = torch.zeros(_lib.WORKSPACE_BYTES // 4, dtype=torch.int32, device=DEV)
+
+    def run(stream):
+        st = stream.cuda_stream
+        _lib.call("tnq_nvfp4_quantize_dynamic", x.data_ptr(), rows, cols, _lib.IN_BF16, ws.data_ptr(), packed.data_ptr(),
+                  sf.data_ptr(), _lib.SCALES_SWIZZLED, gs.data_ptr(), st)
+        _lib.call("tnq_fp8_dynamic_cast_transpose", x.data_ptr(), rows, cols, _lib.IN_BF16, _lib.FP8_E4M3, ws.data_ptr(),
+                  q.data_ptr(), q_t.data_ptr(), scale.data_ptr(), st)
+
+    g = _capture(run)
+    for k in (1.0, 3.0):
+        x.mul_(k)
+        g.replay()
+        torch.cuda.synchronize()
+        xc = x.cpu()
+        wp, wsf, wg = oracle.nvfp4_quantize(xc)
+        assert torch.equal(packed.cpu(), wp) and torch.equal(sf.cpu(), oracle.to_blocked(as_u8(wsf))) and torch.equal(gs.cpu(), wg)
+        want, wscale = oracle.fp8_dynamic_quant(xc, torch.float8_e4m3fn)
+        assert torch.equal(q.cpu(), as_u8(want)) and torch.equal(q_t.cpu(), as_u8(want).t().contiguous())
+        assert torch.equal(scale.cpu(), wscale)
+    assert int(ws[_lib.WS_STATUS_WORD].item()) == 0
