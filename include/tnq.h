@@ -147,8 +147,8 @@ int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dty
                            void* out, void* out_t, uint32_t* status, tnq_stream_t stream);
 
 /* Dynamic-scale form of tnq_fp8_cast_transpose: amax pass into the workspace, then the saturated cast in
- * both layouts with scale = fp8_max / max(amax, 1e-12), tiles walked from the end of the matrix as in
- * tnq_nvfp4_quantize_dynamic.  *scale_out (nullable) receives the scale; status = word 3 of the workspace. */
+ * both layouts with scale = fp8_max / max(amax, 1e-12).  *scale_out (nullable) receives the scale; status =
+ * word 3 of the workspace. */
 int tnq_fp8_dynamic_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,
                                    void* workspace, void* out, void* out_t, float* scale_out,
                                    tnq_stream_t stream);
@@ -323,9 +323,8 @@ int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype,
                        float* global_scale_out, uint32_t* status, tnq_stream_t stream);
 
 /* The same with the tensor-wide amax taken first (dynamic global scale): an amax pass into the workspace
- * (word 1), then the quantizer, which walks the tiles from the END of the matrix - the part the amax pass
- * read last and asked L2 to keep - so that part is not read from HBM a second time (16384 x 16384: 202 ->
- * 192 us for the pair).  x additionally 32-byte aligned; the status word is word 3 of the workspace. */
+ * (word 1), then the quantizer, in one call.  x additionally 32-byte aligned; the status word is word 3 of
+ * the workspace. */
 int tnq_nvfp4_quantize_dynamic(const void* x, int64_t rows, int64_t cols, int in_dtype, void* workspace,
                                void* packed, void* sf, int scale_layout, float* global_scale_out,
                                tnq_stream_t stream);

@@ -198,9 +198,8 @@ def test_tile_copy_diagnostic(shape, stages, per_sm):
 
 
 def test_dynamic_entries_match_their_two_call_forms():
-    """tnq_nvfp4_quantize_dynamic and tnq_fp8_dynamic_cast_transpose (amax pass + tiles walked from the end of the
-    matrix) give the bytes of the amax call followed by the plain entry point (tiles walked from the start),
-    on a matrix larger than L2 and on ragged small ones."""
+    """tnq_nvfp4_quantize_dynamic and tnq_fp8_dynamic_cast_transpose (amax pass + quantizer in one call) give the
+    bytes of the amax call followed by the plain entry point, on a matrix larger than L2 and on ragged small ones."""
     dev = torch.device(DEV, torch.cuda.current_device())
     ws = _lib.workspace(dev)
     stream = _lib.stream_ptr(dev)

@@ -209,7 +209,7 @@ constexpr int kBtSmemBytes = 2 * kStageOutBytes + kBtStages * kTileBytes + 64;
 template <int OUT, bool SAT>
 __global__ void __launch_bounds__(512, 2)
     k_cast_transpose_bt(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap map_col, CastTParams p,
-                        uint32_t tiles_r, uint32_t tiles_c, uint32_t* status, int backwards) {
+                        uint32_t tiles_r, uint32_t tiles_c, uint32_t* status) {
   extern __shared__ __align__(1024) uint8_t tnq_dyn_smem_1k[];
   uint8_t* const base = tnq_dyn_smem_1k;
   const uint32_t stg_t = smem_u32(base);  // transposed staging, read by the TMA store
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(512, 2)
   const uint64_t pol = l2_policy_evict_first();
 
   TileCursor cur, ahead;
-  cur.init(first, gridDim.x, tiles_c, backwards ? ntiles - 1 : 0);
+  cur.init(first, gridDim.x, tiles_c);
   ahead = cur;
   auto issue = [&](uint32_t s) {
     mbar_expect_tx(&bars[s], kTileBytes);
@@ -333,8 +333,7 @@ extern "C" int tnq_cast_transpose_set_store_variant(int v) {
 }
 
 template <int OUT, bool SAT>
-static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream,
-                                    bool backwards) {
+static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
   const int cap = resident_ctas_smem<k_cast_transpose_bt<OUT, SAT>, 512, kBtSmemBytes>();
   if (cap < 1) return cuda_fail(cudaGetLastError());
   CUtensorMap map_col;
@@ -344,19 +343,17 @@ static int launch_cast_transpose_bt(const CUtensorMap& map, const CastTParams& p
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
   return launch_chained(k_cast_transpose_bt<OUT, SAT>, dim3(grid), dim3(512), kBtSmemBytes, stream, map, map_col, p,
-                        (uint32_t)tiles_r, (uint32_t)tiles_c, status, backwards && ntiles > 1 ? 1 : 0);
+                        (uint32_t)tiles_r, (uint32_t)tiles_c, status);
 }
 
 template <int OUT, bool SAT>
-static int launch_cast_transpose_any(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream,
-                                     bool backwards) {
+static int launch_cast_transpose_any(const CUtensorMap& map, const CastTParams& p, uint32_t* status, cudaStream_t stream) {
   if (g_ct_store_variant.load(std::memory_order_relaxed) == 1 && p.rows % 16 == 0 && aligned16(p.out_t))
-    return launch_cast_transpose_bt<OUT, SAT>(map, p, status, stream, backwards);
+    return launch_cast_transpose_bt<OUT, SAT>(map, p, status, stream);
   return launch_cast_transpose<OUT, SAT>(map, p, status, stream);
 }
 
-// amax_workspace != null: the dynamic form - an amax pass into that workspace first (the scale is then read from its
-// word 2), and the tiles walked from the end of the matrix, the part that pass read last and asked L2 to keep.
+// amax_workspace != null: the dynamic form - an amax pass into that workspace first; the scale is then read from its word 2.
 static int cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype, const float* scale,
                           int scale_kind, int saturated, float* abs_max_inout, void* out, void* out_t, uint32_t* status,
                           cudaStream_t stream, void* amax_workspace, float* scale_out) {
@@ -380,17 +377,16 @@ static int cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtyp
   p.abs_max = abs_max_inout;
   p.out = static_cast<uint8_t*>(out), p.out_t = static_cast<uint8_t*>(out_t);
   p.t_aligned = (rows % 32 == 0) && ((reinterpret_cast<uintptr_t>(out_t) & 31u) == 0);
-  const bool dynamic = amax_workspace != nullptr;
-  if (dynamic) {
+  if (amax_workspace != nullptr) {
     rc = amax_pass(x, rows * cols, in_dtype, amax_workspace, scale_out, out_dtype == TNQ_FP8_E4M3 ? 448.0f : 57344.0f, stream,
-                   true);
+                   false);
     if (rc != TNQ_OK) return rc;
   }
   if (out_dtype == TNQ_FP8_E4M3)
-    return saturated ? launch_cast_transpose_any<TNQ_FP8_E4M3, true>(map, p, status, stream, dynamic)
-                     : launch_cast_transpose_any<TNQ_FP8_E4M3, false>(map, p, status, stream, dynamic);
-  return saturated ? launch_cast_transpose_any<TNQ_FP8_E5M2, true>(map, p, status, stream, dynamic)
-                   : launch_cast_transpose_any<TNQ_FP8_E5M2, false>(map, p, status, stream, dynamic);
+    return saturated ? launch_cast_transpose_any<TNQ_FP8_E4M3, true>(map, p, status, stream)
+                     : launch_cast_transpose_any<TNQ_FP8_E4M3, false>(map, p, status, stream);
+  return saturated ? launch_cast_transpose_any<TNQ_FP8_E5M2, true>(map, p, status, stream)
+                   : launch_cast_transpose_any<TNQ_FP8_E5M2, false>(map, p, status, stream);
 }
 
 extern "C" int tnq_fp8_cast_transpose(const void* x, int64_t rows, int64_t cols, int in_dtype, int out_dtype,

@@ -149,8 +149,8 @@ struct Fp4Op {
 
 __global__ void __launch_bounds__(Fp4Op::kThreads, 2)
     k_nvfp4(const __grid_constant__ CUtensorMap tmap, Fp4Params p, uint32_t tiles_r, uint32_t tiles_c, uint32_t* status,
-            int walk) {  // bit 0: evict-first loads, bit 1: tiles from the end of the matrix
-  run_tile_pipeline<Fp4Op>(&tmap, p, tiles_r, tiles_c, status, (walk & 1) != 0, (walk & 2) != 0);
+            int evict_first) {
+  run_tile_pipeline<Fp4Op>(&tmap, p, tiles_r, tiles_c, status, evict_first != 0);
 }
 
 }  // namespace tnq
@@ -186,15 +186,15 @@ static int nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtyp
   const int64_t tiles_r = (rows + kTileRows - 1) / kTileRows, tiles_c = (cols + kTileCols - 1) / kTileCols;
   const int64_t ntiles = tiles_r * tiles_c;
   const int grid = (int)(ntiles < cap ? ntiles : cap);
-  // dynamic global scale: the amax pass first, then the tiles from the end of the matrix, which is the part the amax
-  // pass read last and asked L2 to keep (16384 x 16384: 202 -> 192 us for the two launches)
-  const bool dynamic = amax_workspace != nullptr;
-  if (dynamic) {
-    rc = amax_pass(x, rows * cols, in_dtype, amax_workspace, nullptr, 448.0f, stream, true);
+  // Dynamic global scale: the amax pass first.  Keeping the end of the matrix in L2 for the quantizer and walking
+  // the tiles from that end (what the per-tensor cast does) was measured here and gives nothing: the quantizer then
+  // reads 477 MB instead of 537 MB from HBM and takes the same time, it is not bound by its reads.
+  if (amax_workspace != nullptr) {
+    rc = amax_pass(x, rows * cols, in_dtype, amax_workspace, nullptr, 448.0f, stream, false);
     if (rc != TNQ_OK) return rc;
   }
   return launch_chained(k_nvfp4, dim3(grid), dim3(Fp4Op::kThreads), kTileSmemBytes, stream, map, p, (uint32_t)tiles_r,
-                        (uint32_t)tiles_c, status, (tile_loads_evict_first() ? 1 : 0) | (dynamic && ntiles > 1 ? 2 : 0));
+                        (uint32_t)tiles_c, status, tile_loads_evict_first() ? 1 : 0);
 }
 
 extern "C" int tnq_nvfp4_quantize(const void* x, int64_t rows, int64_t cols, int in_dtype,

@@ -41,29 +41,18 @@ __device__ __forceinline__ uint8_t* tile_smem_base(uint8_t* raw) {
 //                                                across tiles: running maxima live there)
 // Position of a CTA in its tile sequence (tiles blockIdx.x, + gridDim.x, ...), advanced
 // without divisions: 32-bit tile coordinates, the ring stage and its phase bit.
-// `last` != 0 walks the same tiles from the end of the matrix: tile last - first, last - first - stride, ...
-// (last = number of tiles - 1).  Behind an amax pass over the same matrix the end of it is what L2 still holds.
 struct TileCursor {
   uint32_t tr, tc;      // tile row / column
   uint32_t step_r, step_c, tiles_c;
-  bool back;
-  __device__ __forceinline__ void init(uint32_t first, uint32_t stride, uint32_t tiles_c_, uint32_t last = 0) {
+  __device__ __forceinline__ void init(uint32_t first, uint32_t stride, uint32_t tiles_c_) {
     tiles_c = tiles_c_;
-    back = last != 0;
-    if (back) first = last >= first ? last - first : 0;  // a CTA without tiles never uses its cursor
     tr = first / tiles_c, tc = first % tiles_c;
     step_r = stride / tiles_c, step_c = stride % tiles_c;
   }
   __device__ __forceinline__ void advance() {
-    if (back) {  // may run past tile 0 after the CTA's last tile: the wrapped value is never used
-      if (tc < step_c) tc += tiles_c, --tr;
-      tc -= step_c;
-      tr -= step_r;
-    } else {
-      tc += step_c;
-      tr += step_r;
-      if (tc >= tiles_c) tc -= tiles_c, ++tr;
-    }
+    tc += step_c;
+    tr += step_r;
+    if (tc >= tiles_c) tc -= tiles_c, ++tr;
   }
 };
 
@@ -71,7 +60,7 @@ struct TileCursor {
 template <class Op>
 __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const typename Op::Params& p,
                                                   uint32_t tiles_r, uint32_t tiles_c, uint32_t* status,
-                                                  bool evict_first = false, bool backwards = false) {
+                                                  bool evict_first = false) {
   extern __shared__ uint8_t tnq_dyn_smem[];
   uint8_t* const base = tile_smem_base(tnq_dyn_smem);
   uint64_t* const bars = reinterpret_cast<uint64_t*>(base + kStages * kTileBytes);
@@ -92,7 +81,7 @@ __device__ __forceinline__ void run_tile_pipeline(const CUtensorMap* tmap, const
   pdl_launch_dependents();
   typename Op::State state = Op::init(p);
   TileCursor cur, ahead;  // tile being consumed / next tile to load
-  cur.init(first, gridDim.x, tiles_c, backwards ? ntiles - 1 : 0);
+  cur.init(first, gridDim.x, tiles_c);
   ahead = cur;
   const uint64_t pol = l2_policy_evict_first();
   auto load = [&](uint32_t s) {  // thread 0: arm stage s and load the tile at `ahead` into it
