@@ -389,7 +389,7 @@ static int launch_gemv(const void* x, const void* w, const void* x_sf, const voi
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess)
       return cuda_fail(cudaGetLastError());
     configured[dev] = 1;
