@@ -62,9 +62,9 @@ int tnq_last_cuda_error(void);
 int tnq_abi_version(void);
 
 /* Process-wide tuning switches (not part of any result: outputs are identical).
- * TNQ_OPT_CAST_REVERSE (default 1): the cast pass of the dynamic and sharded casts
- * walks the tensor from its end, so that the tail the amax pass left in L2 is re-read
- * from L2 instead of HBM. */
+ * TNQ_OPT_CAST_REVERSE (default 1): for tensors between 96 MiB and 1.5 GiB the cast pass of
+ * the dynamic and sharded casts walks the tensor from its end, so that the tail the amax pass
+ * left in L2 is re-read from L2 instead of HBM (larger tensors: the tail is too small a part). */
 #define TNQ_OPT_CAST_REVERSE 1
 /* TNQ_OPT_FUSED_SMALL (default 1): tnq_fp8_dynamic_cast uses the single-launch kernel
  * that keeps the whole tensor in shared memory when it fits (up to ~33.5 MB). */
