@@ -179,32 +179,7 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
   const uint32_t kb = k / F::kBlock;
   pdl_wait();  // chained launch: nothing of the stream's previous kernel is read or overwritten before this
   pdl_launch_dependents();
-
-  // ---- prologue: decode x once per CTA.  Piece q of chunk c is stored at uint4 index
-  // (c / 32) * 32 * Q + q * 32 + (c % 32), so that the 32 lanes of a warp read consecutive
-  // 16-byte pieces (no bank conflicts).
-  if constexpr (FP4) {
-    for (uint32_t i = threadIdx.x; i < k / 8; i += kGemvThreads) {  // one word = 8 codes = one 16-byte piece
-      uint32_t o[4];
-      cvt_e2m1x8_to_f16x2(reinterpret_cast<const uint32_t*>(x)[i], o);
-      const uint32_t c = i >> 2, q = i & 3;
-      sts128(xs + (((c >> 5) * Q + q) * 32 + (c & 31)) * 16, o[0], o[1], o[2], o[3]);
-    }
-    for (uint32_t i = threadIdx.x; i < kb; i += kGemvThreads)
-      sts32(fx + i * 4, __float_as_uint(e4m3_byte_to_f32(x_sf[sf_row_base(0, kb, layout) + sf_col_offset(i, layout)])));
-  } else {
-    for (uint32_t i = threadIdx.x; i < k / 4; i += kGemvThreads) {  // one word = 4 bytes = half a piece
-      uint32_t lo, hi;
-      cvt_e4m3x4_to_f16x2(reinterpret_cast<const uint32_t*>(x)[i], lo, hi);
-      const uint32_t c = i >> 2, q = (i >> 1) & 1, e = (i & 1) * 2;
-      sts64(xs + ((((c >> 5) * Q + q) * 32 + (c & 31)) * 4 + e) * 4, lo, hi);
-    }
-    for (uint32_t i = threadIdx.x; i < kb; i += kGemvThreads)
-      sts32(fx + i * 4, __float_as_uint(e8m0_to_f32(x_sf[sf_row_base(0, kb, layout) + sf_col_offset(i, layout)])));
-  }
-  __syncthreads();
-  float g = 1.0f;
-  if constexpr (FP4) g = (x_global ? *x_global : 1.0f) * (w_global ? *w_global : 1.0f);
+  float g = 1.0f;  // product of the global scales (NVFP4), read in the prologue
 
   // ---- this warp's work: a balanced contiguous range of row groups.
   // Group g owns rows (g / 32) * 128 + (g % 32) + 32 * r, r = 0..3.
@@ -354,9 +329,35 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
     }
   };
 
-  // ---- the pipeline
+  // ---- the pipeline: the first weight copies leave before x is decoded, so they fly during the prologue
 #pragma unroll
   for (int d = 0; d < S - 1; ++d) issue();
+
+  // ---- prologue: decode x once per CTA.  Piece q of chunk c is stored at uint4 index
+  // (c / 32) * 32 * Q + q * 32 + (c % 32), so that the 32 lanes of a warp read consecutive
+  // 16-byte pieces (no bank conflicts).
+  if constexpr (FP4) {
+    for (uint32_t i = threadIdx.x; i < k / 8; i += kGemvThreads) {  // one word = 8 codes = one 16-byte piece
+      uint32_t o[4];
+      cvt_e2m1x8_to_f16x2(reinterpret_cast<const uint32_t*>(x)[i], o);
+      const uint32_t c = i >> 2, q = i & 3;
+      sts128(xs + (((c >> 5) * Q + q) * 32 + (c & 31)) * 16, o[0], o[1], o[2], o[3]);
+    }
+    for (uint32_t i = threadIdx.x; i < kb; i += kGemvThreads)
+      sts32(fx + i * 4, __float_as_uint(e4m3_byte_to_f32(x_sf[sf_row_base(0, kb, layout) + sf_col_offset(i, layout)])));
+  } else {
+    for (uint32_t i = threadIdx.x; i < k / 4; i += kGemvThreads) {  // one word = 4 bytes = half a piece
+      uint32_t lo, hi;
+      cvt_e4m3x4_to_f16x2(reinterpret_cast<const uint32_t*>(x)[i], lo, hi);
+      const uint32_t c = i >> 2, q = (i >> 1) & 1, e = (i & 1) * 2;
+      sts64(xs + ((((c >> 5) * Q + q) * 32 + (c & 31)) * 4 + e) * 4, lo, hi);
+    }
+    for (uint32_t i = threadIdx.x; i < kb; i += kGemvThreads)
+      sts32(fx + i * 4, __float_as_uint(e8m0_to_f32(x_sf[sf_row_base(0, kb, layout) + sf_col_offset(i, layout)])));
+  }
+  __syncthreads();
+  if constexpr (FP4) g = (x_global ? *x_global : 1.0f) * (w_global ? *w_global : 1.0f);
+
   uint4 sv_cur = make_uint4(0, 0, 0, 0);
   if (!swz) sv_cur = load_raw_scales(c_group, c_kb, c_c);
   for (uint32_t it = 0; it < items; ++it) {
