@@ -138,9 +138,11 @@ def test_chained_launch_sees_the_previous_kernels_output():
         assert torch.equal(swz[i][1].cpu(), oracle.to_blocked(swz[i][0].cpu())), i
 
 
-def test_single_launch_casts_on_two_streams():
-    """Two host threads cast on two streams at once, each with its own workspace: every call's CTAs are placed
-    together although the launches are not cooperative, so no call runs into the bounded wait of its exchange."""
+@pytest.mark.parametrize("n_streams", [2, 4])
+def test_single_launch_casts_on_several_streams(n_streams):
+    """Host threads cast on streams of their own at once, each with its own workspace, every call chained to its
+    predecessor: each call's CTAs are placed together although the launches are not cooperative, so no call runs
+    into the bounded wait of its exchange."""
     import threading
 
     x = make_input("fp8_tensor", "cpu")
@@ -165,13 +167,13 @@ def test_single_launch_casts_on_two_streams():
         except Exception as e:  # pragma: no cover - reported below
             errors.append(e)
 
-    threads = [threading.Thread(target=worker, args=(k,)) for k in range(2)]
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(n_streams)]
     for t in threads:
         t.start()
     for t in threads:
         t.join()
     assert not errors, errors
-    for k in range(2):
+    for k in range(n_streams):
         outs, status = results[k]
         assert status == 0, (k, status)
         for q in outs:
