@@ -6,9 +6,10 @@ TEST INFRASTRUCTURE ONLY.  The reference (drisspg/transformer_nuggets) is pure P
 nothing to compile: "building" it means making its package importable where the checkout itself is
 absent (the machine the GPU benchmark runs on).  ``oracle/_ref/`` is ignored by git - the copy never
 enters this repository's history - but it travels with the working tree like the built
-``libtnq.so``.  Only ``transformer_nuggets/**/*.py`` is copied; nothing is edited.  The benchmark's
-reference arm and CPU-baseline leg import it through ``oracle/reference.py``; no file of the shipped
-package does.
+``libtnq.so``.  Only ``transformer_nuggets/**/*.py`` and the reference's two test files for this path
+(``test/test_fp8.py``, ``test/test_mx.py``) are copied; nothing is edited.  The benchmark's reference arm
+and CPU-baseline leg import the package through ``oracle/reference.py``; ``tests/test_gpu_reference_suite.py``
+runs the two test files against this repository's package; no file of the shipped package touches any of it.
 """
 
 from __future__ import annotations
@@ -42,6 +43,14 @@ def make_ref(ref_root: str) -> str:
             with open(a, "rb") as f:
                 digest.update(os.path.relpath(a, src).encode() + b"\0" + f.read())
             count += 1
+    tests_dst = os.path.join(DEST, "test")
+    if os.path.isdir(tests_dst):
+        shutil.rmtree(tests_dst)
+    for name in ("test_fp8.py", "test_mx.py"):  # the reference's own tests of the cast path, unmodified
+        a = os.path.join(ref_root, "test", name)
+        if os.path.isfile(a):
+            os.makedirs(tests_dst, exist_ok=True)
+            shutil.copyfile(a, os.path.join(tests_dst, name))
     with open(os.path.join(DEST, "SOURCE.txt"), "w") as f:
         f.write(f"unmodified copy of {count} .py files of the reference package transformer_nuggets\n"
                 f"sha256 over (relative path, contents) in sorted order: {digest.hexdigest()}\n")
