@@ -387,6 +387,15 @@ def run_comparators():
     return out
 
 
+def apply_env_options():
+    """TNQ_SET_OPTIONS="option=value,..." -> tnq_set_option, for A/B runs of the tuning switches (include/tnq.h)."""
+    from transformer_nuggets_b200 import _lib
+
+    for item in filter(None, os.environ.get("TNQ_SET_OPTIONS", "").split(",")):
+        opt, val = item.split("=")
+        _lib.call("tnq_set_option", int(opt), int(val))
+
+
 def workload_config(name, n_gpus, exchange, rows=None):
     import dataclasses
 
@@ -490,6 +499,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    apply_env_options()
     cfg = CONFIGS[HEADLINE]
     if args.rows:  # smaller same-shape case for profiler captures
         import dataclasses
@@ -793,9 +803,7 @@ def other_workloads(dev, peak, only=None, iters=None, warm=None):
         _lib.call("tnq_mxfp8_set_store_variant", int(os.environ["TNQ_MX_STORE_VARIANT"]))
     if os.environ.get("TNQ_CT_STORE_VARIANT"):
         _lib.call("tnq_cast_transpose_set_store_variant", int(os.environ["TNQ_CT_STORE_VARIANT"]))
-    for item in filter(None, os.environ.get("TNQ_SET_OPTIONS", "").split(",")):  # "option=value,..." -> tnq_set_option
-        opt, val = item.split("=")
-        _lib.call("tnq_set_option", int(opt), int(val))
+    apply_env_options()
 
     def report(name, ms, note, bytes_per_elem=None):
         cfg = CONFIGS[name]

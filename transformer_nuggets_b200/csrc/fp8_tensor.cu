@@ -359,7 +359,11 @@ __global__ void __launch_bounds__(kThreads)
            int scale_source, float* abs_max_inout, Workspace* ws, ExchangeWait ex, int reverse, int l2_mode) {
   using T = InTraits<IN>;
   __shared__ uint32_t smem32[33];
-  pdl_wait();  // the scale may come from the preceding amax launch
+  // The scale may come from the preceding amax launch: wait for it - except on the exchange path.  There the cast
+  // takes nothing from that launch but the slot words it polls below, and everything older in the stream was complete
+  // before the amax launch got past its own wait.  Without the wait the cast does not sit behind the amax kernel's
+  // completion, which includes the acknowledgement of its stores into the peers' memory (one per rank).
+  if (ex.slots == nullptr || (l2_mode & 8) != 0) pdl_wait();
   pdl_launch_dependents();
   float s;
   if (ex.slots != nullptr) {  // amax of all ranks, read from this GPU's own slots
@@ -461,6 +465,7 @@ static std::atomic<int> g_cast_pair{1};
 static std::atomic<int> g_tile_evict_first{0};  // measured: NVFP4 205.6 -> 209.5 us with it, MXFP8 one direction 31.3 -> 31.1
 static std::atomic<int> g_fused_launch{1};
 static std::atomic<int> g_pdl_chain{1};
+static std::atomic<int> g_exchange_cast_waits{0};
 namespace tnq_host {
 bool pdl_chain() { return g_pdl_chain.load(std::memory_order_relaxed) != 0; }
 int fused_launch_mode() { return g_fused_launch.load(std::memory_order_relaxed); }
@@ -491,6 +496,7 @@ extern "C" int tnq_set_option(int option, int value) {
     case TNQ_OPT_CAST_L2_MODE: g_cast_l2_mode.store(value & 3, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_CAST_PAIR: g_cast_pair.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_TILE_EVICT_FIRST: g_tile_evict_first.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
+    case TNQ_OPT_EXCHANGE_CAST_WAITS: g_exchange_cast_waits.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_PDL_CHAIN: g_pdl_chain.store(value ? 1 : 0, std::memory_order_relaxed); return TNQ_OK;
     case TNQ_OPT_FUSED_LAUNCH:
       if (value != 0 && value != 1) return TNQ_EINVAL;
@@ -586,7 +592,8 @@ static int cast_any(const void* x, void* out, int64_t n, int in_dtype, int out_d
   const bool after_amax = pdl || scale_source == TNQ_SCALE_IS_AMAX;
   const int reverse = (after_amax && g_cast_reverse.load(std::memory_order_relaxed) && reverse_pays(in_bytes)) ? 1 : 0;
   // bit 2: the scale is this very tensor's fp8_max / amax (dynamic and sharded casts), see k_cast
-  const int l2_mode = (reverse ? g_cast_l2_mode.load(std::memory_order_relaxed) : 0) | ((pdl || ex.slots != nullptr) ? 4 : 0);
+  const int l2_mode = (reverse ? g_cast_l2_mode.load(std::memory_order_relaxed) : 0) | ((pdl || ex.slots != nullptr) ? 4 : 0) |
+                      (g_exchange_cast_waits.load(std::memory_order_relaxed) ? 8 : 0);
   const uint8_t* xp = static_cast<const uint8_t*>(x);
   uint8_t* op = static_cast<uint8_t*>(out);
   Workspace* ws = static_cast<Workspace*>(workspace);
