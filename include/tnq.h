@@ -394,6 +394,10 @@ int tnq_nvfp4_gemv(const void* x_packed, const void* w_packed, const void* x_sf,
                    const float* x_global, const float* w_global, int64_t n, int64_t k, int scale_layout,
                    void* y_bf16, tnq_stream_t stream);
 
+/* CTA shape of the two GEMVs: 0 (default) = chosen by N and K, 1 = 128 threads and four ring slots per lane, 2 = 512 threads
+ * and three slots sharing one fp16 copy of x.  Same results either way. */
+int tnq_gemv_set_shape(int shape);
+
 /* Tensor-wide amax of a row-sharded tensor, for quantizers that take the amax as an
  * input (tnq_nvfp4_quantize): local amax -> 8-byte store into every rank's slot buffer ->
  * a one-CTA kernel waits (bounded) for all ranks' words and writes their MAX to

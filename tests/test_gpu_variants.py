@@ -232,3 +232,39 @@ def test_dynamic_entries_match_their_two_call_forms():
     with pytest.raises(_lib.TnqError):
         _lib.call("tnq_fp8_dynamic_cast_transpose", x.data_ptr(), 128, 128, _lib.IN_BF16, _lib.FP8_E4M3, 0, out.data_ptr(),
                   out.data_ptr(), 0, stream)
+
+
+@pytest.mark.parametrize("n,k", [(128, 2048), (264, 4096), (130, 2080), (1024, 16384), (8, 65536)])
+def test_gemv_cta_shapes_agree(n, k):
+    """The two CTA shapes of the block-scaled GEMVs (128 threads x 4 ring slots, 512 threads x 3 slots) give the same
+    bits, raw and swizzled scales, MXFP8 and NVFP4; at K = 65536 the wide shape does not fit and the narrow one runs."""
+    from transformer_nuggets_b200.cute.blockscaled_tma import BlockScaleLayout
+    from transformer_nuggets_b200.cute.mxfp8_tma import mxfp8_tma_gemv
+    from transformer_nuggets_b200.cute.nvfp4_tma import nvfp4_tma_gemv
+
+    g = torch.Generator(device=DEV).manual_seed(n + k)
+    w = torch.randn(n, k, dtype=torch.bfloat16, device=DEV, generator=g)
+    x = torch.randn(1, k, dtype=torch.bfloat16, device=DEV, generator=g)
+    try:
+        outs = {}
+        for shape in (1, 2, 0):
+            _lib.call("tnq_gemv_set_shape", shape)
+            if k % 32 == 0:
+                rw, rx = tn.quantize_mxfp8(w, swizzle=True), tn.quantize_mxfp8(x, swizzle=True)
+                y8 = mxfp8_tma_gemv(rx.q_row, rw.q_row, rx.scale_row, rw.scale_row, block_scale_layout=BlockScaleLayout.SWIZZLE_32_4_4)
+                rw, rx = tn.quantize_mxfp8(w, swizzle=False), tn.quantize_mxfp8(x, swizzle=False)
+                y8r = mxfp8_tma_gemv(rx.q_row, rw.q_row, rx.scale_row, rw.scale_row, block_scale_layout=BlockScaleLayout.RAW)
+            aw, ax = tn.quantize_nvfp4(w), tn.quantize_nvfp4(x)
+            y4 = nvfp4_tma_gemv(ax.packed, aw.packed, ax.block_scales, aw.block_scales, input_global_scale=ax.global_scale,
+                                weight_global_scale=aw.global_scale)
+            outs[shape] = (y8.clone(), y8r.clone(), y4.clone())
+        for shape in (2, 0):
+            for a, b in zip(outs[1], outs[shape]):
+                assert torch.equal(a, b), shape
+        exact = (x.float() @ w.float().t())
+        assert float((outs[0][0].float() - exact).abs().mean() / exact.abs().mean()) < 0.08
+        assert float((outs[0][2].float() - exact).abs().mean() / exact.abs().mean()) < 0.2
+    finally:
+        _lib.call("tnq_gemv_set_shape", 0)
+    with pytest.raises(_lib.TnqError):
+        _lib.call("tnq_gemv_set_shape", 3)

@@ -44,6 +44,7 @@ SIGNATURES = {
     "tnq_fp8_rowwise": [_p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p],
     "tnq_rowwise_set_tma": [_i],
     "tnq_rowwise_set_group": [_i],
+    "tnq_gemv_set_shape": [_i],
     "tnq_mxfp8_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "tnq_mxfp8_set_store_variant": [_i],
     "tnq_nvfp4_quantize": [_p, _i64, _i64, _i, _p, _p, _p, _i, _p, _p, _p],
@@ -164,7 +165,7 @@ def require_cuda(t: torch.Tensor, what: str):
 
 
 #: entry points that launch nothing (no status to look at afterwards)
-_NO_LAUNCH = {"tnq_set_option", "tnq_mxfp8_set_store_variant", "tnq_cast_transpose_set_store_variant", "tnq_rowwise_set_tma", "tnq_rowwise_set_group", "tnq_exchange_create",
+_NO_LAUNCH = {"tnq_set_option", "tnq_gemv_set_shape", "tnq_mxfp8_set_store_variant", "tnq_cast_transpose_set_store_variant", "tnq_rowwise_set_tma", "tnq_rowwise_set_group", "tnq_exchange_create",
               "tnq_exchange_open", "tnq_exchange_close", "tnq_exchange_destroy", "tnq_exchange_status"}
 
 #: most recently used (device, stream) -> workspace; bounded so that a program that keeps creating

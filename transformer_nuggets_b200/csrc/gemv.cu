@@ -23,6 +23,8 @@
 // one 32 x 32 -> 64-bit multiply-add per copy.  Lanes are folded with shuffles at the end
 // of a row group; every output row is produced by one warp in a fixed order, so results do
 // not depend on the grid.
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -30,19 +32,16 @@
 
 namespace tnq {
 
-#ifndef TNQ_GEMV_THREADS
-#define TNQ_GEMV_THREADS 128
-#endif
-#ifndef TNQ_GEMV_MIN_CTAS
-#define TNQ_GEMV_MIN_CTAS 4
-#endif
-constexpr int kGemvThreads = TNQ_GEMV_THREADS;
-constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kGemvRows = 4;  // rows per warp and step
-#ifndef TNQ_GEMV_STAGES
-#define TNQ_GEMV_STAGES 4
-#endif
-constexpr int kGemvStages = TNQ_GEMV_STAGES;  // slots per lane ring: kGemvStages - 1 steps of copies in flight
+// Two shapes of CTA.  The fp16 copy of x (2 bytes per element of K) is per CTA, so a long K leaves room for few
+// small CTAs: "narrow" = 128 threads and 4 ring slots per lane (3 steps of copies in flight; four CTAs per SM while
+// x is short), "wide" = 512 threads and 3 slots sharing one copy of x (16 warps per SM whatever K is).
+struct GemvNarrow {
+  static constexpr int kThreads = 128, kStages = 4, kMinCtas = 4;
+};
+struct GemvWide {
+  static constexpr int kThreads = 512, kStages = 3, kMinCtas = 1;
+};
 
 // 2^(byte - 127) as fp32; byte 0 -> 2^-127 (subnormal), byte 255 -> NaN
 __device__ __forceinline__ float e8m0_to_f32(uint32_t byte) {
@@ -144,10 +143,10 @@ __host__ __device__ constexpr int gemv_x_bytes(int k) {
 }
 
 // ---------------------------------------------------------------- the kernel
-// One warp owns one row group at a time.  Every lane keeps a private ring of kGemvStages
+// One warp owns one row group at a time.  Every lane keeps a private ring of C::kStages
 // slots in shared memory; a slot holds the lane's 16-byte chunk of each of the four rows and
 // (swizzled layout) the 16-byte piece with the rows' scale bytes.  Slots are filled with
-// cp.async (one commit group per step) kGemvStages - 1 steps ahead of consumption, so the
+// cp.async (one commit group per step) C::kStages - 1 steps ahead of consumption, so the
 // bytes in flight are bounded by shared memory rather than by registers or by the order in
 // which register loads retire, and no lane ever reads a slot another lane wrote: the
 // pipeline needs neither a barrier nor a warp synchronisation.
@@ -162,15 +161,15 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <bool FP4>
-__global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
+template <bool FP4, class C>
+__global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
     k_blockscaled_gemv(const uint8_t* __restrict__ w, const uint8_t* __restrict__ x, const uint8_t* __restrict__ x_sf,
                        const uint8_t* __restrict__ w_sf, const float* __restrict__ x_global,
                        const float* __restrict__ w_global, uint32_t n, uint32_t k, int layout,
                        uint16_t* __restrict__ y) {
   using F = GemvFmt<FP4>;
   constexpr int Q = FP4 ? 4 : 2;  // 16-byte pieces of fp16 x per 16-byte weight chunk
-  constexpr int S = kGemvStages;
+  constexpr int S = C::kStages, kGemvThreads = C::kThreads, kGemvWarps = C::kThreads / 32;
   extern __shared__ __align__(16) uint8_t tnq_gemv_smem[];
   const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t ring = smem_u32(tnq_gemv_smem) + warp * (S * kSlotBytes) + lane * 16;  // this lane's ring
@@ -380,33 +379,64 @@ __global__ void __launch_bounds__(kGemvThreads, TNQ_GEMV_MIN_CTAS)
 using namespace tnq;
 using namespace tnq_host;
 
-template <bool FP4>
-static int launch_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg, const float* wg,
-                       int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
+template <bool FP4, class C>
+static int launch_gemv_shape(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg, const float* wg,
+                             int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
   using F = GemvFmt<FP4>;
+  constexpr int kWarps = C::kThreads / 32;
   const int kb = (int)(k / F::kBlock);
-  const int smem = kGemvWarps * kGemvStages * kSlotBytes + gemv_x_bytes<FP4>((int)k) + ((kb + 3) & ~3) * 4;
+  const int smem = kWarps * C::kStages * kSlotBytes + gemv_x_bytes<FP4>((int)k) + ((kb + 3) & ~3) * 4;
   static int configured[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess)
       return cuda_fail(cudaGetLastError());
     configured[dev] = 1;
   }
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_blockscaled_gemv<FP4>, kGemvThreads, smem) !=
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_blockscaled_gemv<FP4, C>, C::kThreads, smem) !=
           cudaSuccess ||
       per_sm < 1)
     return TNQ_EUNSUPPORTED;
   const int64_t groups = ((n + 127) / 128) * 32;
-  const int64_t want = (groups + kGemvWarps - 1) / kGemvWarps;
+  const int64_t want = (groups + kWarps - 1) / kWarps;
   const int64_t cap = (int64_t)per_sm * sm_count();
   const int grid = (int)(want < cap ? want : cap);
-  return launch_chained(k_blockscaled_gemv<FP4>, dim3(grid), dim3(kGemvThreads), smem, stream, static_cast<const uint8_t*>(w),
+  return launch_chained(k_blockscaled_gemv<FP4, C>, dim3(grid), dim3(C::kThreads), smem, stream, static_cast<const uint8_t*>(w),
                         static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(x_sf), static_cast<const uint8_t*>(w_sf), xg,
                         wg, (uint32_t)n, (uint32_t)k, layout, static_cast<uint16_t*>(y));
+}
+
+// shape: 0 = by N and K (see gemv_wide_pays), 1 = narrow, 2 = wide
+static std::atomic<int> g_gemv_shape{0};
+extern "C" int tnq_gemv_set_shape(int shape) {
+  if (shape < 0 || shape > 2) return TNQ_EINVAL;
+  g_gemv_shape.store(shape, std::memory_order_relaxed);
+  return TNQ_OK;
+}
+// Measured on 256 MiB of weights, two matrices in turn (us, narrow / wide): MXFP8 K = 2048 49.9 / 44.3, 4096 47.1 /
+// 43.8, 8192 (N = 32768) 48.7 / 48.1, 12288 54.8 / 50.7, 16384 56.7 / 49.9, 32768 57.5 / 47.4; NVFP4 K = 2048 56.4 / 53.3,
+// 8192 (N = 65536) 58.1 / 53.9, 16384 (N = 32768) 59.6 / 63.5, 24576 65.1 / 63.1, 32768 69.9 / 60.0.  The wide shape
+// keeps sixteen warps per SM whatever K is, but hands out whole row groups to four times fewer, larger units: with
+// fewer than four groups per warp the uneven split costs more than the occupancy gains, unless K is so long that
+// the narrow shape is down to one or two CTAs per SM.
+static bool gemv_wide_pays(bool fp4, int64_t n, int64_t k) {
+  const int64_t groups = ((n + 127) / 128) * 32, wide_warps = (int64_t)sm_count() * (GemvWide::kThreads / 32);
+  return k >= (fp4 ? 24576 : 12288) || groups >= 4 * wide_warps;
+}
+
+template <bool FP4>
+static int launch_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg, const float* wg,
+                       int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
+  const int shape = g_gemv_shape.load(std::memory_order_relaxed);
+  const bool wide = shape == 2 || (shape == 0 && gemv_wide_pays(FP4, n, k));
+  if (wide) {
+    const int rc = launch_gemv_shape<FP4, GemvWide>(x, w, x_sf, w_sf, xg, wg, n, k, layout, y, stream);
+    if (rc != TNQ_EUNSUPPORTED) return rc;  // x too long for sixteen rings beside it: the narrow shape
+  }
+  return launch_gemv_shape<FP4, GemvNarrow>(x, w, x_sf, w_sf, xg, wg, n, k, layout, y, stream);
 }
 
 extern "C" int tnq_mxfp8_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, int64_t n, int64_t k,
