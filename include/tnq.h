@@ -394,8 +394,9 @@ int tnq_nvfp4_gemv(const void* x_packed, const void* w_packed, const void* x_sf,
                    const float* x_global, const float* w_global, int64_t n, int64_t k, int scale_layout,
                    void* y_bf16, tnq_stream_t stream);
 
-/* CTA shape of the two GEMVs: 0 (default) = chosen by N and K, 1 = 128 threads and four ring slots per lane, 2 = 512 threads
- * and three slots sharing one fp16 copy of x.  Same results either way. */
+/* CTA shape of the two GEMVs: 0 (default) and 2 = 512 threads and three ring slots per lane sharing one fp16 copy
+ * of x (128 threads where that does not fit: K = 65536), 1 = 128 threads and four slots.  The shapes cut the rows'
+ * sums at different steps: results agree to an fp32 rounding of the sums. */
 int tnq_gemv_set_shape(int shape);
 
 /* Tensor-wide amax of a row-sharded tensor, for quantizers that take the amax as an

@@ -236,8 +236,9 @@ def test_dynamic_entries_match_their_two_call_forms():
 
 @pytest.mark.parametrize("n,k", [(128, 2048), (264, 4096), (130, 2080), (1024, 16384), (8, 65536)])
 def test_gemv_cta_shapes_agree(n, k):
-    """The two CTA shapes of the block-scaled GEMVs (128 threads x 4 ring slots, 512 threads x 3 slots) give the same
-    bits, raw and swizzled scales, MXFP8 and NVFP4; at K = 65536 the wide shape does not fit and the narrow one runs."""
+    """The two CTA shapes of the block-scaled GEMVs (128 threads x 4 ring slots, 512 threads x 3 slots) agree to a
+    bf16 rounding (they cut the rows' sums at different steps), raw and swizzled scales, MXFP8 and NVFP4; at K = 65536
+    the wide shape does not fit and the narrow one runs."""
     from transformer_nuggets_b200.cute.blockscaled_tma import BlockScaleLayout
     from transformer_nuggets_b200.cute.mxfp8_tma import mxfp8_tma_gemv
     from transformer_nuggets_b200.cute.nvfp4_tma import nvfp4_tma_gemv
@@ -260,7 +261,8 @@ def test_gemv_cta_shapes_agree(n, k):
             outs[shape] = (y8.clone(), y8r.clone(), y4.clone())
         for shape in (2, 0):
             for a, b in zip(outs[1], outs[shape]):
-                assert torch.equal(a, b), shape
+                torch.testing.assert_close(a, b, rtol=2.0 ** -7, atol=1e-2)
+        assert torch.equal(outs[0][0], outs[0][1])  # swizzled and raw scales: the same kernel, the same cuts
         exact = (x.float() @ w.float().t())
         assert float((outs[0][0].float() - exact).abs().mean() / exact.abs().mean()) < 0.08
         assert float((outs[0][2].float() - exact).abs().mean() / exact.abs().mean()) < 0.2

@@ -21,8 +21,8 @@
 // the mixed-precision FMA (fma.rn.f32.f16), NVFP4 sums the eight products of a half block
 // exactly in fp16x2 (|sum| <= 288) before widening, and all per-row address arithmetic is
 // one 32 x 32 -> 64-bit multiply-add per copy.  Lanes are folded with shuffles at the end
-// of a row group; every output row is produced by one warp in a fixed order, so results do
-// not depend on the grid.
+// of a row group; an output row is the sum of at most two warps' parts added in a fixed order, so a
+// result is reproducible for a given shape and GPU (where the work is cut depends on the number of SMs).
 #include <atomic>
 
 #include <cuda_bf16.h>
@@ -180,16 +180,33 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   pdl_launch_dependents();
   float g = 1.0f;  // product of the global scales (NVFP4), read in the prologue
 
-  // ---- this warp's work: a balanced contiguous range of row groups.
-  // Group g owns rows (g / 32) * 128 + (g % 32) + 32 * r, r = 0..3.
+  // ---- this warp's work.  Group g owns rows (g / 32) * 128 + (g % 32) + 32 * r, r = 0..3; an item is one 512-byte
+  // step of one group.  The CTAs split the groups evenly; inside a CTA the warps split its ITEMS evenly, so a
+  // warp's range may begin and end inside a group.  Such a group belongs to two warps (a CTA with at least as many
+  // groups as warps gives every warp at least `steps` items, so never to three): the later warp, which meets the
+  // group's last steps at the very start of its range, leaves its four partial sums in shared memory; the earlier
+  // warp, which reaches the group's first steps at the end of its range, adds them to its own (first part + second
+  // part, a fixed order) and stores the rows.  CTAs with fewer groups than warps split whole groups.
   const uint32_t row_bytes = k / F::kElemsPerByte;
   const uint32_t chunks = row_bytes / 16;     // 16-byte chunks per row
   const uint32_t steps = (chunks + 31) / 32;  // 512-byte steps per row (the last may be ragged)
   const uint32_t groups = ((n + 127) / 128) * 32;
-  const uint32_t warps = gridDim.x * kGemvWarps, gw = blockIdx.x * kGemvWarps + warp;
-  const uint32_t g_begin = (uint32_t)((uint64_t)gw * groups / warps);
-  const uint32_t g_end = (uint32_t)((uint64_t)(gw + 1) * groups / warps);
-  const uint32_t items = (g_end - g_begin) * steps;
+  const uint32_t cta_g0 = (uint32_t)((uint64_t)blockIdx.x * groups / gridDim.x);
+  const uint32_t cta_ng = (uint32_t)((uint64_t)(blockIdx.x + 1) * groups / gridDim.x) - cta_g0;
+  uint32_t item_a, item_b;  // this warp's items within the CTA: item = (group - cta_g0) * steps + step
+  if (cta_ng >= (uint32_t)kGemvWarps) {
+    item_a = (uint32_t)((uint64_t)warp * cta_ng * steps / kGemvWarps);
+    item_b = (uint32_t)((uint64_t)(warp + 1) * cta_ng * steps / kGemvWarps);
+  } else {
+    item_a = (warp * cta_ng / kGemvWarps) * steps;
+    item_b = ((warp + 1) * cta_ng / kGemvWarps) * steps;
+  }
+  const uint32_t items = item_b - item_a;
+  const uint32_t g_begin = cta_g0 + item_a / steps, first_step = item_a % steps;
+  const bool starts_inside = first_step != 0;           // the group's earlier steps belong to the previous warp
+  __shared__ float s_part[32][kGemvRows];               // [warp]: partial sums of the group a warp starts inside
+  __shared__ uint32_t s_part_ready[32];
+  if (threadIdx.x < 32) s_part_ready[threadIdx.x] = 0;  // ordered before any use by the barrier behind the prologue
   const bool swz = layout == TNQ_SCALES_SWIZZLED;
   const uint32_t kb0 = FP4 ? 2 * lane : lane >> 1;  // first block column of this lane's chunk in step 0
   const uint32_t kb_step = FP4 ? 64 : 16;           // block columns a step advances
@@ -197,7 +214,8 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   const uint32_t ktiles = (kb + 3) >> 2;
 
   // producer cursor: the group's (clamped) rows and scale base, the lane's chunk and block column
-  uint32_t l_group = g_begin, l_step = 0, l_c = lane, l_kb = kb0, l_item = 0, l_slot = 0;
+  uint32_t l_group = g_begin, l_step = first_step, l_c = lane + 32 * first_step, l_kb = kb0 + kb_step * first_step, l_item = 0,
+           l_slot = 0;
   uint32_t l_row[kGemvRows];
   const uint8_t* l_sf = w_sf;
   auto enter_group = [&]() {
@@ -208,9 +226,9 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   };
   enter_group();
   uint4 sv_next = make_uint4(0, 0, 0, 0);  // raw layout: the scale bytes of the step after the one being consumed
-  auto load_raw_scales = [&](uint32_t group, uint32_t kbcol, uint32_t c) {
+  auto load_raw_scales = [&](bool in_range, uint32_t group, uint32_t kbcol, uint32_t c) {
     uint32_t v[kGemvRows] = {0, 0, 0, 0};
-    if (group < g_end && c < chunks) {
+    if (in_range && c < chunks) {
       const uint32_t row0 = (group >> 5) * 128 + (group & 31);
 #pragma unroll
       for (int r = 0; r < kGemvRows; ++r) {
@@ -241,8 +259,8 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   float acc[kGemvRows];
 #pragma unroll
   for (int r = 0; r < kGemvRows; ++r) acc[r] = 0.0f;
-  uint32_t c_group = g_begin, c_step = 0, c_c = lane, c_kb = kb0, c_slot = 0;
-  uint32_t xi = lane;  // uint4 index of this lane's first x piece
+  uint32_t c_group = g_begin, c_step = first_step, c_c = lane + 32 * first_step, c_kb = kb0 + kb_step * first_step, c_slot = 0;
+  uint32_t xi = lane + Q * 32 * first_step;  // uint4 index of this lane's first x piece of the step
   auto consume = [&](const uint4& sv_raw) {
     if (c_c >= chunks) return;
     const uint32_t slot = ring + c_slot * kSlotBytes;
@@ -304,10 +322,11 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
       }
     }
   };
-  auto step_done = [&]() {
+  auto step_done = [&](bool last_item) {
     c_c += 32, c_kb += kb_step, xi += Q * 32;
     if (++c_slot == S) c_slot = 0;
-    if (++c_step == steps) {  // end of the group: fold the lanes, lane r stores row r
+    const bool group_end = ++c_step == steps;
+    if (group_end || last_item) {  // end of the group, or of this warp's part of it: fold the lanes, lane r takes row r
 #pragma unroll
       for (int r = 0; r < kGemvRows; ++r) {
         float v = acc[r];
@@ -315,12 +334,26 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         acc[r] = v;
       }
-      const uint32_t row = (c_group >> 5) * 128 + (c_group & 31) + 32 * lane;
-      if (lane < kGemvRows && row < n) {
-        float v = acc[0];
+      float v = acc[0];
 #pragma unroll
-        for (int r = 1; r < kGemvRows; ++r) v = lane == r ? acc[r] : v;
-        y[row] = __bfloat16_as_ushort(__float2bfloat16_rn(FP4 ? __fmul_rn(v, g) : v));
+      for (int r = 1; r < kGemvRows; ++r) v = lane == r ? acc[r] : v;
+      if (starts_inside && c_group == g_begin) {
+        // the group's later steps, met first: leave the partial sums for the previous warp
+        if (lane < kGemvRows) s_part[warp][lane] = v;
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          *reinterpret_cast<volatile uint32_t*>(&s_part_ready[warp]) = 1u;
+        }
+      } else {
+        if (!group_end) {  // this warp's range ends inside the group: the next warp left the rest long ago
+          for (uint32_t spin = 0; spin < (1u << 26); ++spin)
+            if (*reinterpret_cast<volatile uint32_t*>(&s_part_ready[warp + 1]) != 0u) break;
+          __threadfence_block();
+          if (lane < kGemvRows) v = __fadd_rn(v, *reinterpret_cast<volatile float*>(&s_part[warp + 1][lane]));
+        }
+        const uint32_t row = (c_group >> 5) * 128 + (c_group & 31) + 32 * lane;
+        if (lane < kGemvRows && row < n) y[row] = __bfloat16_as_ushort(__float2bfloat16_rn(FP4 ? __fmul_rn(v, g) : v));
       }
 #pragma unroll
       for (int r = 0; r < kGemvRows; ++r) acc[r] = 0.0f;
@@ -358,17 +391,17 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   if constexpr (FP4) g = (x_global ? *x_global : 1.0f) * (w_global ? *w_global : 1.0f);
 
   uint4 sv_cur = make_uint4(0, 0, 0, 0);
-  if (!swz) sv_cur = load_raw_scales(c_group, c_kb, c_c);
+  if (!swz) sv_cur = load_raw_scales(items > 0, c_group, c_kb, c_c);
   for (uint32_t it = 0; it < items; ++it) {
     issue();  // refills the slot consumed in the previous iteration
     if (!swz) {  // raw scale bytes cannot go through 16-byte copies: keep them one step ahead in registers
       uint32_t ng = c_group, nk = c_kb + kb_step, nc = c_c + 32;
       if (c_step + 1 == steps) ng = c_group + 1, nk = kb0, nc = lane;
-      sv_next = load_raw_scales(ng, nk, nc);
+      sv_next = load_raw_scales(it + 1 < items, ng, nk, nc);
     }
     cp_async_wait<S - 1>();  // everything but the S - 1 newest groups has landed: this item's slot is ready
     consume(sv_cur);
-    step_done();
+    step_done(it + 1 == items);
     sv_cur = sv_next;
   }
   cp_async_wait<0>();
@@ -390,7 +423,7 @@ static int launch_gemv_shape(const void* x, const void* w, const void* x_sf, con
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+    if (cudaFuncSetAttribute(k_blockscaled_gemv<FP4, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
         cudaSuccess)
       return cuda_fail(cudaGetLastError());
     configured[dev] = 1;
@@ -409,29 +442,26 @@ static int launch_gemv_shape(const void* x, const void* w, const void* x_sf, con
                         wg, (uint32_t)n, (uint32_t)k, layout, static_cast<uint16_t*>(y));
 }
 
-// shape: 0 = by N and K (see gemv_wide_pays), 1 = narrow, 2 = wide
+// shape: 0 = wide where it fits and the matrix has rows enough (default), 1 = narrow, 2 = wide (narrow if it does not fit)
 static std::atomic<int> g_gemv_shape{0};
 extern "C" int tnq_gemv_set_shape(int shape) {
   if (shape < 0 || shape > 2) return TNQ_EINVAL;
   g_gemv_shape.store(shape, std::memory_order_relaxed);
   return TNQ_OK;
 }
-// Measured on 256 MiB of weights, two matrices in turn (us, narrow / wide): MXFP8 K = 2048 49.9 / 44.3, 4096 47.1 /
-// 43.8, 8192 (N = 32768) 48.7 / 48.1, 12288 54.8 / 50.7, 16384 56.7 / 49.9, 32768 57.5 / 47.4; NVFP4 K = 2048 56.4 / 53.3,
-// 8192 (N = 65536) 58.1 / 53.9, 16384 (N = 32768) 59.6 / 63.5, 24576 65.1 / 63.1, 32768 69.9 / 60.0.  The wide shape
-// keeps sixteen warps per SM whatever K is, but hands out whole row groups to four times fewer, larger units: with
-// fewer than four groups per warp the uneven split costs more than the occupancy gains, unless K is so long that
-// the narrow shape is down to one or two CTAs per SM.
-static bool gemv_wide_pays(bool fp4, int64_t n, int64_t k) {
-  const int64_t groups = ((n + 127) / 128) * 32, wide_warps = (int64_t)sm_count() * (GemvWide::kThreads / 32);
-  return k >= (fp4 ? 24576 : 12288) || groups >= 4 * wide_warps;
-}
-
+// Measured on 256 MiB of weights, two matrices in turn (us, narrow / wide): MXFP8 K = 2048 45.9 / 45.0, 4096 47.4 /
+// 44.7, 8192 46.6 / 44.6, 16384 48.5 / 45.3, 32768 57.1 / 49.3; NVFP4 K = 2048 58.8 / 55.0, 8192 57.4 / 54.3, 16384
+// 65.6 / 56.1, 32768 67.5 / 57.1.  The wide shape keeps sixteen warps per SM whatever K is; it is the default and the
+// narrow one takes over where sixteen rings and the copy of x no longer fit (K = 65536) and for matrices with too
+// few rows to give most SMs a wide CTA of their own (MXFP8 4096 x 4096: 6.4 / 8.8 us, 1024 x 8192: 8.0 / 13.8).  Before the warps of a CTA
+// split its items at step granularity the wide shape lost to the uneven split of whole row groups (3.5 groups per
+// warp at N = 32768: MXFP8 K = 8192 48.7 / 48.1, NVFP4 K = 16384 59.6 / 63.5).
 template <bool FP4>
 static int launch_gemv(const void* x, const void* w, const void* x_sf, const void* w_sf, const float* xg, const float* wg,
                        int64_t n, int64_t k, int layout, void* y, cudaStream_t stream) {
   const int shape = g_gemv_shape.load(std::memory_order_relaxed);
-  const bool wide = shape == 2 || (shape == 0 && gemv_wide_pays(FP4, n, k));
+  const int64_t groups = ((n + 127) / 128) * 32;  // wide CTAs wanted: one per sixteen row groups
+  const bool wide = shape == 2 || (shape == 0 && groups * 20 >= (int64_t)sm_count() * 16 * 17);  // >= 0.85 per SM
   if (wide) {
     const int rc = launch_gemv_shape<FP4, GemvWide>(x, w, x_sf, w_sf, xg, wg, n, k, layout, y, stream);
     if (rc != TNQ_EUNSUPPORTED) return rc;  // x too long for sixteen rings beside it: the narrow shape
