@@ -1179,6 +1179,27 @@ def _bench_gemv(dev, res, timed, peak, stream, which=None):
     nbytes = n * k * (0.5 + 1 / 16) + k * (0.5 + 1 / 16) + 2 * n
     res["gemv_nvfp4"] = report(timed(f4, [aw2, aw]) * 1e3, nbytes,
                                f"N={n} K={k}, swizzled E4M3 scales + global scales, two 256 MiB weight matrices in turn")
+    # the same product with row-major scales, the layout the reference's GEMV entry points take by default
+    from transformer_nuggets_b200.cute.nvfp4_tma import quantize_nvfp4
+
+    x_raw = quantize_nvfp4(x, swizzle=False)
+    raws = []
+    for wq in (aw2, aw):  # swizzled -> raw on the device: undo the 128x4 atoms of the [n, k / 16] scale matrix
+        sc = wq.block_scales.view(torch.uint8).view(n // 128, k // 64, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(n, k // 16)
+        raws.append((wq, sc.contiguous()))
+
+    def f4r(pair):
+        _lib.call("tnq_nvfp4_gemv", x_raw.packed.data_ptr(), pair[0].packed.data_ptr(), x_raw.block_scales.data_ptr(),
+                  pair[1].data_ptr(), x_raw.global_scale.data_ptr(), pair[0].global_scale.data_ptr(), n, k, _lib.SCALES_RAW,
+                  y.data_ptr(), stream)
+
+    y_swz = y.clone()
+    f4(aw)
+    torch.cuda.synchronize()
+    y_swz.copy_(y)
+    res["gemv_nvfp4_raw_scales"] = report(timed(f4r, raws) * 1e3, nbytes,
+                                          f"N={n} K={k}, row-major E4M3 scales, two weight matrices in turn")
+    res["gemv_nvfp4_raw_scales"]["same_bits_as_swizzled"] = bool(torch.equal(y, y_swz))
 
 
 def _bench_fp8_tensor(dev, res, timed, report, ws, stream):

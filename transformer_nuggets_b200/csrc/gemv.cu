@@ -149,7 +149,9 @@ __host__ __device__ constexpr int gemv_x_bytes(int k) {
 // cp.async (one commit group per step) C::kStages - 1 steps ahead of consumption, so the
 // bytes in flight are bounded by shared memory rather than by registers or by the order in
 // which register loads retire, and no lane ever reads a slot another lane wrote: the
-// pipeline needs neither a barrier nor a warp synchronisation.
+// pipeline needs neither a barrier nor a warp synchronisation for the weights.  The scale pieces of a step are copied
+// once per warp and read across lanes, with a warp synchronisation on either side (one copy per lane, as the weights,
+// moved every swizzled piece two (NVFP4) or eight (MXFP8) times: NVFP4 54.6 -> 50 us).
 constexpr int kSlotBytes = (kGemvRows + 1) * 512;  // per warp: 4 rows x 512 B + 512 B of scale pieces
 
 __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* g) {
@@ -207,7 +209,13 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   __shared__ float s_part[32][kGemvRows];               // [warp]: partial sums of the group a warp starts inside
   __shared__ uint32_t s_part_ready[32];
   if (threadIdx.x < 32) s_part_ready[threadIdx.x] = 0;  // ordered before any use by the barrier behind the prologue
+  // bit 2 of `layout` (set by the launcher): raw scales whose rows are 16-byte aligned and whole steps long, so
+  // that a step's scale bytes of a row are whole 16-byte pieces and can travel through the rings as well
+  const bool rawq = (layout & 4) != 0;
+  layout &= 3;
   const bool swz = layout == TNQ_SCALES_SWIZZLED;
+  const bool shared_sf = swz || rawq;             // scale pieces copied once per warp and read across lanes
+  constexpr uint32_t kSfPieces = FP4 ? 16u : 4u;  // 16-byte scale pieces per step
   const uint32_t kb0 = FP4 ? 2 * lane : lane >> 1;  // first block column of this lane's chunk in step 0
   const uint32_t kb_step = FP4 ? 64 : 16;           // block columns a step advances
   const uint32_t sh = swz ? (kb0 & 3) * 8 : 0;      // where this lane's scale byte(s) sit in a scale word
@@ -225,6 +233,12 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
     if (swz) l_sf = w_sf + ((uint64_t)(row0 >> 7) * ktiles) * 512 + (row0 & 31) * 16;
   };
   enter_group();
+  auto l_row_of = [&](uint32_t r) {
+    uint32_t v = l_row[0];
+#pragma unroll
+    for (int i = 1; i < kGemvRows; ++i) v = r == (uint32_t)i ? l_row[i] : v;
+    return v;
+  };
   uint4 sv_next = make_uint4(0, 0, 0, 0);  // raw layout: the scale bytes of the step after the one being consumed
   auto load_raw_scales = [&](bool in_range, uint32_t group, uint32_t kbcol, uint32_t c) {
     uint32_t v[kGemvRows] = {0, 0, 0, 0};
@@ -245,7 +259,18 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
       const uint8_t* wp = w + (uint64_t)l_c * 16;
 #pragma unroll
       for (int r = 0; r < kGemvRows; ++r) cp_async16(slot + r * 512, wp + (uint64_t)l_row[r] * row_bytes);
-      if (swz) cp_async16(slot + kGemvRows * 512, l_sf + (uint64_t)(l_kb >> 2) * 512);
+    }
+    // The step's scale bytes: 4 rows x 16 (MXFP8) / 64 (NVFP4) block columns = 4 / 16 pieces of 16 bytes, copied once
+    // by the first 4 / 16 lanes, each into its own piece of the slot's scale area, and read by the whole warp.
+    if (shared_sf && l_item < items && lane < kSfPieces) {
+      const uint32_t step_kb = l_kb - kb0;  // first block column of the step
+      const uint32_t dst = ring + l_slot * kSlotBytes + kGemvRows * 512;
+      if (swz) {  // piece p: the four rows' bytes for block columns 4 p .. 4 p + 3 of the step
+        if ((step_kb >> 2) + lane < ktiles) cp_async16(dst, l_sf + (uint64_t)((step_kb >> 2) + lane) * 512);
+      } else {  // raw: lane 4 r + q (NVFP4) / r (MXFP8) copies the q-th 16 bytes of row r
+        const uint32_t r = FP4 ? lane >> 2 : lane, q = FP4 ? lane & 3u : 0u;
+        cp_async16(dst, w_sf + (uint64_t)l_row_of(r) * kb + step_kb + 16u * q);
+      }
     }
     cp_async_commit();
     ++l_item, l_c += 32, l_kb += kb_step;
@@ -264,7 +289,18 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   auto consume = [&](const uint4& sv_raw) {
     if (c_c >= chunks) return;
     const uint32_t slot = ring + c_slot * kSlotBytes;
-    const uint4 sv = swz ? lds128(slot + kGemvRows * 512) : sv_raw;
+    const uint32_t area = slot - lane * 16 + kGemvRows * 512;  // the warp's scale area of this slot
+    // swizzled: the piece with this lane's block column(s): two lanes (NVFP4) / eight lanes (MXFP8) share one
+    uint4 sv = swz ? lds128(area + (FP4 ? lane >> 1 : lane >> 3) * 16) : sv_raw;
+    if (rawq) {  // row r's step bytes at 64 r (NVFP4, two bytes per lane) / 16 r (MXFP8)
+      uint32_t v[kGemvRows];
+#pragma unroll
+      for (int r = 0; r < kGemvRows; ++r) {
+        if constexpr (FP4) asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v[r]) : "r"(area + 64 * r + 2 * lane));
+        else asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v[r]) : "r"(area + 16 * r + (lane >> 1)));
+      }
+      sv = make_uint4(v[0], v[1], v[2], v[3]);
+    }
     const uint32_t sw[kGemvRows] = {sv.x >> sh, sv.y >> sh, sv.z >> sh, sv.w >> sh};
     if constexpr (FP4) {
       uint4 xv[4];
@@ -391,15 +427,17 @@ __global__ void __launch_bounds__(C::kThreads, C::kMinCtas)
   if constexpr (FP4) g = (x_global ? *x_global : 1.0f) * (w_global ? *w_global : 1.0f);
 
   uint4 sv_cur = make_uint4(0, 0, 0, 0);
-  if (!swz) sv_cur = load_raw_scales(items > 0, c_group, c_kb, c_c);
+  if (!shared_sf) sv_cur = load_raw_scales(items > 0, c_group, c_kb, c_c);
   for (uint32_t it = 0; it < items; ++it) {
+    if (shared_sf) __syncwarp();  // every lane has read the scale pieces of the slot that is refilled next
     issue();  // refills the slot consumed in the previous iteration
-    if (!swz) {  // raw scale bytes cannot go through 16-byte copies: keep them one step ahead in registers
+    if (!shared_sf) {  // raw scale bytes that cannot go through 16-byte copies: one step ahead in registers
       uint32_t ng = c_group, nk = c_kb + kb_step, nc = c_c + 32;
       if (c_step + 1 == steps) ng = c_group + 1, nk = kb0, nc = lane;
       sv_next = load_raw_scales(it + 1 < items, ng, nk, nc);
     }
     cp_async_wait<S - 1>();  // everything but the S - 1 newest groups has landed: this item's slot is ready
+    if (shared_sf) __syncwarp();   // ... for every lane: the scale pieces are read across lanes
     consume(sv_cur);
     step_done(it + 1 == items);
     sv_cur = sv_next;
@@ -437,9 +475,13 @@ static int launch_gemv_shape(const void* x, const void* w, const void* x_sf, con
   const int64_t want = (groups + kWarps - 1) / kWarps;
   const int64_t cap = (int64_t)per_sm * sm_count();
   const int grid = (int)(want < cap ? want : cap);
+  // raw scales ride the copy rings when every row's scale bytes of a step are whole, aligned 16-byte pieces:
+  // rows of whole 512-byte steps (K % 512 == 0 for MXFP8, % 1024 for NVFP4) and a 16-byte aligned buffer
+  const int64_t chunks = k / F::kElemsPerByte / 16;
+  const bool rawq = layout == TNQ_SCALES_RAW && chunks % 32 == 0 && kb % 16 == 0 && aligned16(w_sf);
   return launch_chained(k_blockscaled_gemv<FP4, C>, dim3(grid), dim3(C::kThreads), smem, stream, static_cast<const uint8_t*>(w),
                         static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(x_sf), static_cast<const uint8_t*>(w_sf), xg,
-                        wg, (uint32_t)n, (uint32_t)k, layout, static_cast<uint16_t*>(y));
+                        wg, (uint32_t)n, (uint32_t)k, layout | (rawq ? 4 : 0), static_cast<uint16_t*>(y));
 }
 
 // shape: 0 = wide where it fits and the matrix has rows enough (default), 1 = narrow, 2 = wide (narrow if it does not fit)
