@@ -427,6 +427,9 @@ __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
 // Programmatic dependent launch: wait for the grid this one depends on / let the
 // dependent grid start its prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_if(bool wait) {  // the wait as one predicated instruction
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %0, 0;\n\t@p griddepcontrol.wait;\n\t}" ::"r"((uint32_t)wait) : "memory");
+}
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
